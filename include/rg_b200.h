@@ -1,0 +1,179 @@
+/*
+ * rg_b200.h - C ABI of the B200 (sm_100a) GPT token-loop library.
+ *
+ * Every entry point is what a foreign-function binding for RustyGradients
+ * (crate rusty-gradients 0.2.0) would bind for this path: plain pointers and
+ * sizes, opaque handles, a status code per call.  The comment above each
+ * declaration names the reference interface it replaces (file:line inside the
+ * crate).  Host pointers are borrowed for the duration of the call only.
+ *
+ * Threading: an rg_ctx may be used from any thread, one call at a time per
+ * context; an rg_gpt has a single owner (the reference's model is !Send,
+ * src/tensor.rs:23).  One context per GPU.
+ */
+#ifndef RG_B200_H
+#define RG_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define RG_API __attribute__((visibility("default")))
+#else
+#define RG_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- errors: src/error.rs:13-50 (RustyGradientsError) plus the two variants
+ * the reference's CUDA backend assumes, src/backend/cuda.rs:41-45,50 -------- */
+typedef enum rg_status {
+    RG_OK = 0,
+    RG_ERR_SHAPE = 1,         /* ShapeError / ShapeMismatch            */
+    RG_ERR_DIMENSION = 2,     /* DimensionError {expected, actual}     */
+    RG_ERR_INVALID_INPUT = 3, /* InvalidInput (id >= vocab, T > block) */
+    RG_ERR_BACKEND = 4,       /* BackendError (CUDA / NCCL failure)    */
+    RG_ERR_UNSUPPORTED = 5,   /* where the reference has unimplemented!() (src/backend/cuda.rs:436-494) */
+    RG_ERR_CONTEXT_FULL = 6,  /* decode past block_size (the reference slides its window, src/wasm_api.rs:103) */
+    RG_ERR_TIMEOUT = 7        /* a bounded device-side wait gave up    */
+} rg_status;
+
+/* Message of the last failing call on this thread (maps to the String payload
+ * of the enum variants above). Never NULL. */
+RG_API const char* rg_last_error(void);
+RG_API const char* rg_version(void);
+
+typedef struct rg_ctx rg_ctx;         /* CudaBackend, src/backend/cuda.rs:77-83       */
+typedef struct rg_storage rg_storage; /* CudaStorage {data, shape, device}, src/backend/cuda.rs:29-33 */
+typedef struct rg_gpt rg_gpt;         /* GPTModel, src/models/gpt.rs:17-24            */
+
+/* ---- context ------------------------------------------------------------ */
+/* CudaBackend::device_count / is_available, src/backend/cuda.rs:128-135 */
+RG_API int rg_device_count(void);
+/* CudaBackend::new(device_index), src/backend/cuda.rs:87-125; Device::cuda(index), src/backend/mod.rs:72-77 */
+RG_API rg_status rg_ctx_create(int device, rg_ctx** out);
+RG_API rg_status rg_ctx_destroy(rg_ctx* ctx);
+/* Backend::synchronize, src/backend/mod.rs:137-138 */
+RG_API rg_status rg_synchronize(rg_ctx* ctx);
+/* The cudaStream_t every call of this context enqueues on (for event timing). */
+RG_API void* rg_ctx_stream(rg_ctx* ctx);
+/* Number of kernels this context has launched since creation. */
+RG_API uint64_t rg_ctx_launch_count(rg_ctx* ctx);
+
+/* ---- storage: Backend memory operations, src/backend/mod.rs:140-155 ---------- */
+/* Backend::zeros / ones */
+RG_API rg_status rg_zeros(rg_ctx* ctx, const size_t* shape, int ndim, rg_storage** out);
+RG_API rg_status rg_ones(rg_ctx* ctx, const size_t* shape, int ndim, rg_storage** out);
+/* Backend::from_slice(&[f32], &[usize]); len != prod(shape) is RG_ERR_SHAPE (src/backend/cpu.rs:54-57) */
+RG_API rg_status rg_from_slice(rg_ctx* ctx, const float* data, size_t len, const size_t* shape, int ndim,
+                        rg_storage** out);
+/* Backend::to_vec: copies prod(shape) floats to out (cap = capacity in floats) and synchronises */
+RG_API rg_status rg_to_vec(rg_ctx* ctx, const rg_storage* st, float* out, size_t cap);
+/* Backend::shape */
+RG_API rg_status rg_shape(const rg_storage* st, size_t* shape_out, int cap, int* ndim_out);
+RG_API size_t rg_storage_len(const rg_storage* st); /* CudaStorage::len, src/backend/cuda.rs:65-67 */
+RG_API rg_status rg_storage_free(rg_storage* st);   /* Drop of the Storage value         */
+
+/* ---- ops: one per Backend trait method, src/backend/mod.rs:157-226.  Each
+ * returns a new owned storage; inputs are never modified. ------------------ */
+/* add / sub / mul with numpy-style broadcasting (src/backend/cpu.rs:68-80; bias add
+ * [B,T,N]+[1,N], 0-D scale and residuals on the model path, src/ops/basic_ops.rs:45-148) */
+RG_API rg_status rg_add(rg_ctx* ctx, const rg_storage* a, const rg_storage* b, rg_storage** out);
+RG_API rg_status rg_sub(rg_ctx* ctx, const rg_storage* a, const rg_storage* b, rg_storage** out);
+RG_API rg_status rg_mul(rg_ctx* ctx, const rg_storage* a, const rg_storage* b, rg_storage** out);
+/* matmul 2Dx2D, 3Dx3D, 4Dx4D (src/backend/cpu.rs:82-208) and 3Dx2D (src/ops/matmul.rs:51-72) */
+RG_API rg_status rg_matmul(rg_ctx* ctx, const rg_storage* a, const rg_storage* b, rg_storage** out);
+/* relu / sigmoid / exp / log / powf (src/backend/cpu.rs:213-244; kernels src/backend/cuda_kernels.cu:81-171) */
+RG_API rg_status rg_relu(rg_ctx* ctx, const rg_storage* a, rg_storage** out);
+RG_API rg_status rg_sigmoid(rg_ctx* ctx, const rg_storage* a, rg_storage** out);
+RG_API rg_status rg_exp(rg_ctx* ctx, const rg_storage* a, rg_storage** out);
+RG_API rg_status rg_log(rg_ctx* ctx, const rg_storage* a, rg_storage** out);
+RG_API rg_status rg_powf(rg_ctx* ctx, const rg_storage* a, float power, rg_storage** out);
+/* tanh-GELU: fused::gelu_fused, src/backend/fused.rs:151-175; kernel gelu_forward,
+ * src/backend/cuda_kernels.cu:120-131 (loaded by the reference but never given a trait method) */
+RG_API rg_status rg_gelu(rg_ctx* ctx, const rg_storage* a, rg_storage** out);
+/* softmax over the last axis, max-subtracted (src/backend/cpu.rs:246-270; src/backend/cuda.rs:404-432) */
+RG_API rg_status rg_softmax(rg_ctx* ctx, const rg_storage* a, rg_storage** out);
+/* sum -> shape [1] (src/backend/cpu.rs:274-277), sum_axis (src/backend/cpu.rs:279-291) */
+RG_API rg_status rg_sum(rg_ctx* ctx, const rg_storage* a, rg_storage** out);
+RG_API rg_status rg_sum_axis(rg_ctx* ctx, const rg_storage* a, size_t axis, rg_storage** out);
+/* reshape (element count must match, src/backend/cpu.rs:292-296) and transpose of two axes,
+ * materialised (src/backend/cpu.rs:298-311) */
+RG_API rg_status rg_reshape(rg_ctx* ctx, const rg_storage* a, const size_t* new_shape, int ndim, rg_storage** out);
+RG_API rg_status rg_transpose(rg_ctx* ctx, const rg_storage* a, size_t axis1, size_t axis2, rg_storage** out);
+/* embedding: f32-valued indices [B,T] or [B], weights [V,D] (src/backend/cpu.rs:315-363) */
+RG_API rg_status rg_embedding(rg_ctx* ctx, const rg_storage* indices, const rg_storage* weights, rg_storage** out);
+/* layer_norm over the last axis, one-pass Welford statistics, biased variance,
+ * eps inside the sqrt (src/backend/cpu.rs:365-375 -> src/backend/fused.rs:22-144); gamma/beta hold D values */
+RG_API rg_status rg_layer_norm(rg_ctx* ctx, const rg_storage* x, const rg_storage* gamma, const rg_storage* beta,
+                        float epsilon, rg_storage** out);
+/* sparse_cross_entropy: mean over rows of -log softmax(logits)[target] (src/backend/cpu.rs:377-427) */
+RG_API rg_status rg_sparse_cross_entropy(rg_ctx* ctx, const rg_storage* logits, const rg_storage* targets,
+                                  rg_storage** out);
+
+/* ---- GPT model: src/models/gpt.rs ---------------------------------------- */
+enum { RG_ACT_RELU = 0, RG_ACT_GELU_TANH = 1 };
+enum { RG_DTYPE_F32 = 0, RG_DTYPE_BF16 = 1 };
+
+/* GptConfig (src/models/gpt.rs:8-14) plus the switches this engine adds. */
+typedef struct rg_gpt_config {
+    size_t block_size;
+    size_t vocab_size;
+    size_t num_layers;
+    size_t num_heads;
+    size_t embedding_dim;
+    int causal;        /* 0: the reference's unmasked attention (src/nn/attention.rs:78-94); 1: causal, enables the KV cache */
+    int activation;    /* RG_ACT_RELU (src/nn/feedforward.rs:43-45) or RG_ACT_GELU_TANH (src/backend/fused.rs:151-175) */
+    int weight_dtype;  /* RG_DTYPE_F32, or RG_DTYPE_BF16: matrices, tables and KV cache kept in bf16 */
+    size_t max_batch;  /* sequences the KV cache is sized for */
+} rg_gpt_config;
+
+/* GPTModel::new(config), src/models/gpt.rs:27-54 (asserts embedding_dim % num_heads == 0, src/nn/attention.rs:38-41) */
+RG_API rg_status rg_gpt_create(rg_ctx* ctx, const rg_gpt_config* cfg, rg_gpt** out);
+RG_API rg_status rg_gpt_destroy(rg_gpt* m);
+/* Module::parameters() order, src/models/gpt.rs:85-93: number of tensors (2 + 16 L + 4) and the shape of tensor i */
+RG_API int rg_gpt_num_params(const rg_gpt* m);
+RG_API rg_status rg_gpt_param_shape(const rg_gpt* m, int i, size_t shape_out[2]);
+/* Weight ingest with the shape asserts of WasmGptTrainer::loadWeightsFromJson,
+ * src/wasm_api.rs:182-199: n tensors in parameters() order, f32, W as [in,out]. */
+RG_API rg_status rg_gpt_load_params(rg_gpt* m, const float* const* data, const size_t* const* shapes,
+                             const int* ndims, int n);
+/* Module::forward(&idx) -> logits, src/models/gpt.rs:58-83: idx_f32 [B,T] host (ids carried as
+ * f32 like src/wasm_api.rs:106), logits [B,T,V] host.  Honours cfg.causal / activation. */
+RG_API rg_status rg_gpt_forward(rg_gpt* m, const float* idx_f32, size_t B, size_t T, float* logits);
+/* First half of the token loop (src/wasm_api.rs:103-118) for a causal model: runs the
+ * prompt [B,T] once, fills the KV cache, leaves position = T.  Optional outputs:
+ * last-row logits [B,V] and their argmax [B] (host). */
+RG_API rg_status rg_gpt_prefill(rg_gpt* m, const uint32_t* ids, size_t B, size_t T, float* logits_last,
+                         uint32_t* argmax);
+/* One iteration of the loop body (src/wasm_api.rs:102-160) on the KV cache: feeds
+ * tok[B] (host) at the current position, returns logits [B,V] (or NULL) and the
+ * greedy pick [B] (or NULL). */
+RG_API rg_status rg_gpt_decode_step(rg_gpt* m, const uint32_t* tok, float* logits, uint32_t* argmax);
+/* WasmGptTrainer::generate(prompt_ids, max_new_tokens, temperature, top_k),
+ * src/wasm_api.rs:97-163, batched over B prompts of equal length P; out [B,max_new].
+ * top_k == 1 is greedy (argmax, lowest index on ties).  Other top_k draw from a
+ * counter-based generator seeded with `seed` (the reference uses thread_rng). */
+RG_API rg_status rg_gpt_generate(rg_gpt* m, const uint32_t* prompt, size_t B, size_t P, size_t max_new,
+                          float temperature, size_t top_k, uint64_t seed, uint32_t* out);
+/* Device-resident greedy loop: n_steps iterations of the loop body starting from the
+ * pick left by prefill / the previous step, ids never leave the GPU.  Asynchronous. */
+RG_API rg_status rg_gpt_decode_run(rg_gpt* m, size_t n_steps);
+/* Rewind the position to T (the cache rows below T stay valid) and make `tok[B]`
+ * (host) the next token to feed. */
+RG_API rg_status rg_gpt_rewind(rg_gpt* m, size_t T, const uint32_t* tok);
+/* Copy generated ids [B, n] starting at absolute position `from` to the host; synchronises. */
+RG_API rg_status rg_gpt_read_tokens(rg_gpt* m, size_t from, size_t n, uint32_t* out);
+RG_API size_t rg_gpt_position(const rg_gpt* m);
+/* Forget the cached context (start of a new generate call). */
+RG_API rg_status rg_gpt_reset(rg_gpt* m);
+/* Algorithmic bytes one decode step reads at context length T for B sequences
+ * (weights + biases + LN + one table row pair + K/V of every cached position). */
+RG_API double rg_gpt_decode_step_bytes(const rg_gpt* m, size_t B, double mean_ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RG_B200_H */

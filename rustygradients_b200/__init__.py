@@ -1,0 +1,12 @@
+"""B200-native GPT token loop behind RustyGradients' Backend / GPT model interface.
+
+The arithmetic lives in lib/librg_b200.so (CUDA, sm_100a, C ABI in
+include/rg_b200.h); this package is the thin host-side mirror of the reference's
+`Backend` trait, `GptConfig`, `GPTModel` and `generate`."""
+from ._lib import (BackendError, ContextFull, DeviceTimeout, DimensionError, InvalidInput,
+                   RustyGradientsError, ShapeError, Unsupported)
+from .backend import B200Backend, Storage
+from .gpt import GptConfig, GPTModel
+
+__all__ = ["B200Backend", "Storage", "GptConfig", "GPTModel", "RustyGradientsError", "ShapeError",
+           "DimensionError", "InvalidInput", "BackendError", "Unsupported", "ContextFull", "DeviceTimeout"]

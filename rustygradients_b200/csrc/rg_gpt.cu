@@ -1,0 +1,764 @@
+// GPT model half of the C ABI: weight ingest, full forward, prompt pass, the
+// KV-cache token step and the generate loop.  Mirrors GptConfig / GPTModel
+// (src/models/gpt.rs) and WasmGptTrainer::generate (src/wasm_api.rs:97-163).
+#include "rg_internal.cuh"
+#include "rg_gemm.cuh"
+#include "rg_decode_kernels.cuh"
+#include "rg_prefill_kernels.cuh"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+
+struct rg_linear {
+    void* W = nullptr;  // [K][ldw] f32 or bf16
+    long long ldw = 0;
+    float* b = nullptr;  // [N]
+    int K = 0, N = 0;
+    int ksplit = 1, krows = 0;  // split of the token-step projection
+    float* parts = nullptr;     // [ksplit][Bmax][N]
+};
+
+struct rg_layer {
+    rg_linear qkv, o, fc1, fc2;
+    float *ln1g = nullptr, *ln1b = nullptr, *ln2g = nullptr, *ln2b = nullptr;
+};
+
+struct rg_gpt {
+    rg_ctx* ctx = nullptr;
+    rg_gpt_config cfg;
+    int V = 0, D = 0, L = 0, H = 0, hd = 0, C = 0, F = 0, Bmax = 1;
+    bool bf16 = false, loaded = false;
+    size_t wsize = 4;
+    long long ldt = 0;  // leading dimension of the two embedding tables
+    void *wte = nullptr, *wpe = nullptr;
+    float *lnfg = nullptr, *lnfb = nullptr;
+    rg_linear head;
+    std::vector<rg_layer> layers;
+    std::vector<void*> allocs;
+
+    // KV cache: [L][Bmax][H][C][hd], f32 or bf16
+    char *kc = nullptr, *vc = nullptr;
+    size_t kv_layer_bytes = 0;
+
+    // token-step state
+    float *xa = nullptr, *xb = nullptr, *ap = nullptr, *logits = nullptr;
+    uint32_t *tokens = nullptr, *picks = nullptr;
+    int *d_pos = nullptr, *d_pos_next = nullptr;
+    int NS = 1;
+    size_t pos = 0, curB = 0;
+    cudaGraphExec_t graph = nullptr;
+    size_t graphB = 0;
+    int kernels_per_step = 0;
+    bool use_graph = true;
+
+    // prompt-pass buffers, grown on demand
+    size_t rowsCap = 0;
+    float *px = nullptr, *pln = nullptr, *pqkv = nullptr, *pattn = nullptr, *ph = nullptr, *plast = nullptr;
+    float* plogits = nullptr;
+    size_t plogitsCap = 0;
+};
+
+static __global__ void rg_set_int2_kernel(int* a, int* b, int v) {
+    *a = v;
+    if (b) *b = v;
+}
+
+// ---------------------------------------------------------------------------
+// allocation helpers
+// ---------------------------------------------------------------------------
+static rg_status dalloc(rg_gpt* m, void** p, size_t bytes) {
+    *p = nullptr;
+    cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+    if (e != cudaSuccess)
+        return rg_fail(RG_ERR_BACKEND, "Failed to allocate %zu bytes of CUDA memory: %s", bytes, cudaGetErrorString(e));
+    m->allocs.push_back(*p);
+    return RG_OK;
+}
+static void dfree(rg_gpt* m, void* p) {
+    if (!p) return;
+    auto it = std::find(m->allocs.begin(), m->allocs.end(), p);
+    if (it != m->allocs.end()) m->allocs.erase(it);
+    cudaFree(p);
+}
+static long long round_up(long long a, long long b) { return (a + b - 1) / b * b; }
+
+static int batch_tile(int B) { return B <= 1 ? 1 : (B <= 2 ? 2 : (B <= 4 ? 4 : 8)); }
+
+static void plan_split(rg_gpt* m, rg_linear& lin) {
+    const int NT = m->bf16 ? 256 : 128;
+    const int ntiles = rg_cdiv(lin.N, NT);
+    int ks = std::max(1, m->ctx->sm_count / ntiles);
+    ks = std::min(ks, std::max(1, lin.K / 16));
+    ks = std::min(ks, 32);
+    lin.krows = (int)round_up(rg_cdiv(lin.K, ks), 8);
+    lin.ksplit = rg_cdiv(lin.K, lin.krows);
+}
+
+static rg_status alloc_linear(rg_gpt* m, rg_linear& lin, int K, int N) {
+    lin.K = K, lin.N = N;
+    lin.ldw = round_up(N, 8);
+    RG_TRY(dalloc(m, &lin.W, (size_t)K * lin.ldw * m->wsize));
+    RG_CUDA(cudaMemset(lin.W, 0, (size_t)K * lin.ldw * m->wsize));
+    RG_TRY(dalloc(m, (void**)&lin.b, (size_t)N * 4));
+    plan_split(m, lin);
+    RG_TRY(dalloc(m, (void**)&lin.parts, (size_t)lin.ksplit * m->Bmax * N * 4));
+    return RG_OK;
+}
+
+// ---------------------------------------------------------------------------
+// create / destroy
+// ---------------------------------------------------------------------------
+template <typename F>
+static void set_smem_attr(F f, int bytes) {
+    cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+extern "C" rg_status rg_gpt_create(rg_ctx* ctx, const rg_gpt_config* cfg, rg_gpt** out) {
+    if (!ctx || !cfg || !out) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    *out = nullptr;
+    if (!cfg->block_size || !cfg->vocab_size || !cfg->num_layers || !cfg->num_heads || !cfg->embedding_dim)
+        return rg_fail(RG_ERR_INVALID_INPUT, "GptConfig fields must be non-zero");
+    if (cfg->embedding_dim % cfg->num_heads != 0)
+        return rg_fail(RG_ERR_INVALID_INPUT, "embed_dim must be divisible by num_heads (%zu %% %zu != 0)",
+                       cfg->embedding_dim, cfg->num_heads);
+    const size_t hd = cfg->embedding_dim / cfg->num_heads;
+    if (hd != 32 && hd != 64 && hd != 128)
+        return rg_fail(RG_ERR_UNSUPPORTED, "head_dim %zu not supported (32, 64 or 128)", hd);
+    if (cfg->activation != RG_ACT_RELU && cfg->activation != RG_ACT_GELU_TANH)
+        return rg_fail(RG_ERR_INVALID_INPUT, "unknown activation %d", cfg->activation);
+    if (cfg->weight_dtype != RG_DTYPE_F32 && cfg->weight_dtype != RG_DTYPE_BF16)
+        return rg_fail(RG_ERR_INVALID_INPUT, "unknown weight_dtype %d", cfg->weight_dtype);
+    if (cfg->vocab_size >= (1u << 24))
+        return rg_fail(RG_ERR_UNSUPPORTED, "vocab_size %zu: ids are carried as f32 and must stay below 2^24", cfg->vocab_size);
+    rg_ctx_guard g(ctx);
+    rg_gpt* m = new rg_gpt();
+    m->ctx = ctx;
+    m->cfg = *cfg;
+    m->V = (int)cfg->vocab_size, m->D = (int)cfg->embedding_dim, m->L = (int)cfg->num_layers;
+    m->H = (int)cfg->num_heads, m->hd = (int)hd, m->C = (int)cfg->block_size, m->F = 4 * m->D;
+    m->Bmax = (int)std::max<size_t>(1, cfg->max_batch);
+    m->bf16 = cfg->weight_dtype == RG_DTYPE_BF16;
+    m->wsize = m->bf16 ? 2 : 4;
+    m->ldt = round_up(m->D, 8);
+    const char* ng = getenv("RG_B200_NO_GRAPH");
+    m->use_graph = !(ng && ng[0] == '1');
+
+    rg_status st = RG_OK;
+    auto TRY = [&](rg_status s) {
+        if (st == RG_OK) st = s;
+    };
+    TRY(dalloc(m, &m->wte, (size_t)m->V * m->ldt * m->wsize));
+    TRY(dalloc(m, &m->wpe, (size_t)m->C * m->ldt * m->wsize));
+    TRY(dalloc(m, (void**)&m->lnfg, m->D * 4));
+    TRY(dalloc(m, (void**)&m->lnfb, m->D * 4));
+    m->layers.resize(m->L);
+    for (int l = 0; l < m->L && st == RG_OK; l++) {
+        rg_layer& y = m->layers[l];
+        TRY(alloc_linear(m, y.qkv, m->D, 3 * m->D));
+        TRY(alloc_linear(m, y.o, m->D, m->D));
+        TRY(alloc_linear(m, y.fc1, m->D, m->F));
+        TRY(alloc_linear(m, y.fc2, m->F, m->D));
+        TRY(dalloc(m, (void**)&y.ln1g, m->D * 4));
+        TRY(dalloc(m, (void**)&y.ln1b, m->D * 4));
+        TRY(dalloc(m, (void**)&y.ln2g, m->D * 4));
+        TRY(dalloc(m, (void**)&y.ln2b, m->D * 4));
+    }
+    if (st == RG_OK) TRY(alloc_linear(m, m->head, m->D, m->V));
+    const size_t kvsize = m->bf16 ? 2 : 4;
+    m->kv_layer_bytes = (size_t)m->Bmax * m->H * m->C * m->hd * kvsize;
+    TRY(dalloc(m, (void**)&m->kc, m->kv_layer_bytes * m->L));
+    TRY(dalloc(m, (void**)&m->vc, m->kv_layer_bytes * m->L));
+    // split of the context across CTAs in the token-step attention
+    m->NS = std::max(1, std::min(16, rg_cdiv(ctx->sm_count, m->H)));
+    TRY(dalloc(m, (void**)&m->xa, (size_t)m->Bmax * m->D * 4));
+    TRY(dalloc(m, (void**)&m->xb, (size_t)m->Bmax * m->D * 4));
+    TRY(dalloc(m, (void**)&m->ap, (size_t)m->Bmax * m->H * m->NS * (m->hd + 2) * 4));
+    TRY(dalloc(m, (void**)&m->logits, (size_t)m->Bmax * m->V * 4));
+    TRY(dalloc(m, (void**)&m->tokens, (size_t)m->Bmax * m->C * 4));
+    TRY(dalloc(m, (void**)&m->picks, (size_t)m->Bmax * 4));
+    TRY(dalloc(m, (void**)&m->d_pos, 16));
+    if (st != RG_OK) {
+        rg_gpt_destroy(m);
+        return st;
+    }
+    m->d_pos_next = m->d_pos + 1;
+    cudaMemset(m->d_pos, 0, 16);
+    cudaMemset(m->tokens, 0, (size_t)m->Bmax * m->C * 4);
+
+    const int big = 100 * 1024;
+    set_smem_attr(rg_gemv_kernel<float, 1>, big);
+    set_smem_attr(rg_gemv_kernel<float, 2>, big);
+    set_smem_attr(rg_gemv_kernel<float, 4>, big);
+    set_smem_attr(rg_gemv_kernel<float, 8>, big);
+    set_smem_attr(rg_gemv_kernel<__nv_bfloat16, 1>, big);
+    set_smem_attr(rg_gemv_kernel<__nv_bfloat16, 2>, big);
+    set_smem_attr(rg_gemv_kernel<__nv_bfloat16, 4>, big);
+    set_smem_attr(rg_gemv_kernel<__nv_bfloat16, 8>, big);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        rg_gpt_destroy(m);
+        return rg_fail(RG_ERR_BACKEND, "kernel attribute setup failed: %s (is the library built for this GPU?)",
+                       cudaGetErrorString(e));
+    }
+    *out = m;
+    return RG_OK;
+}
+
+extern "C" rg_status rg_gpt_destroy(rg_gpt* m) {
+    if (!m) return RG_OK;
+    cudaSetDevice(m->ctx->device);
+    cudaStreamSynchronize(m->ctx->stream);
+    if (m->graph) cudaGraphExecDestroy(m->graph);
+    for (void* p : m->allocs) cudaFree(p);
+    delete m;
+    return RG_OK;
+}
+
+extern "C" int rg_gpt_num_params(const rg_gpt* m) { return m ? 2 + 16 * m->L + 4 : 0; }
+
+extern "C" rg_status rg_gpt_param_shape(const rg_gpt* m, int i, size_t s[2]) {
+    if (!m || !s) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    const int n = rg_gpt_num_params(m);
+    if (i < 0 || i >= n) return rg_fail(RG_ERR_INVALID_INPUT, "parameter index %d out of range 0..%d", i, n - 1);
+    const size_t V = m->V, D = m->D, C = m->C, F = m->F;
+    if (i == 0) { s[0] = V, s[1] = D; return RG_OK; }
+    if (i == 1) { s[0] = C, s[1] = D; return RG_OK; }
+    if (i >= n - 4) {
+        const int j = i - (n - 4);
+        if (j < 2) s[0] = 1, s[1] = D;
+        else if (j == 2) s[0] = D, s[1] = V;
+        else s[0] = 1, s[1] = V;
+        return RG_OK;
+    }
+    const int j = (i - 2) % 16;
+    switch (j) {
+        case 0: case 2: case 4: case 6: s[0] = D, s[1] = D; break;
+        case 10: s[0] = D, s[1] = F; break;
+        case 11: s[0] = 1, s[1] = F; break;
+        case 12: s[0] = F, s[1] = D; break;
+        default: s[0] = 1, s[1] = D; break;
+    }
+    return RG_OK;
+}
+
+// ---------------------------------------------------------------------------
+// weight ingest
+// ---------------------------------------------------------------------------
+static inline uint16_t f32_to_bf16_rne(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);  // NaN
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+
+// Copy a row-major [rows][cols] f32 host matrix into columns [col0, col0+cols) of a
+// device matrix with leading dimension ld, converting to the weight dtype.
+static rg_status upload_matrix(rg_gpt* m, void* dst, long long ld, int col0, const float* src, int rows, int cols) {
+    if (!m->bf16) {
+        RG_CUDA(cudaMemcpy2D((float*)dst + col0, ld * 4, src, (size_t)cols * 4, (size_t)cols * 4, rows,
+                             cudaMemcpyHostToDevice));
+    } else {
+        std::vector<uint16_t> tmp((size_t)rows * cols);
+        for (size_t i = 0; i < tmp.size(); i++) tmp[i] = f32_to_bf16_rne(src[i]);
+        RG_CUDA(cudaMemcpy2D((uint16_t*)dst + col0, ld * 2, tmp.data(), (size_t)cols * 2, (size_t)cols * 2, rows,
+                             cudaMemcpyHostToDevice));
+    }
+    return RG_OK;
+}
+static rg_status upload_vec(float* dst, const float* src, int n) {
+    RG_CUDA(cudaMemcpy(dst, src, (size_t)n * 4, cudaMemcpyHostToDevice));
+    return RG_OK;
+}
+
+extern "C" rg_status rg_gpt_load_params(rg_gpt* m, const float* const* data, const size_t* const* shapes,
+                                        const int* ndims, int n) {
+    if (!m || !data || !shapes || !ndims) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    const int want = rg_gpt_num_params(m);
+    if (n != want)
+        return rg_fail(RG_ERR_SHAPE, "Mismatch in number of parameter tensors during loading: got %d, model has %d", n, want);
+    for (int i = 0; i < n; i++) {
+        size_t s[2];
+        rg_gpt_param_shape(m, i, s);
+        if (!data[i] || !shapes[i]) return rg_fail(RG_ERR_INVALID_INPUT, "parameter %d is NULL", i);
+        if (ndims[i] != 2 || shapes[i][0] != s[0] || shapes[i][1] != s[1])
+            return rg_fail(RG_ERR_SHAPE, "Mismatch in tensor shape during loading: parameter %d expected [%zu, %zu]", i, s[0],
+                           s[1]);
+    }
+    rg_ctx_guard g(m->ctx);
+    RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    const int D = m->D, F = m->F, V = m->V, C = m->C;
+    RG_TRY(upload_matrix(m, m->wte, m->ldt, 0, data[0], V, D));
+    RG_TRY(upload_matrix(m, m->wpe, m->ldt, 0, data[1], C, D));
+    for (int l = 0; l < m->L; l++) {
+        const float* const* p = data + 2 + 16 * l;
+        rg_layer& y = m->layers[l];
+        for (int j = 0; j < 3; j++) {  // Wq | Wk | Wv side by side: one [D,3D] projection
+            RG_TRY(upload_matrix(m, y.qkv.W, y.qkv.ldw, j * D, p[2 * j], D, D));
+            RG_TRY(upload_vec(y.qkv.b + j * D, p[2 * j + 1], D));
+        }
+        RG_TRY(upload_matrix(m, y.o.W, y.o.ldw, 0, p[6], D, D));
+        RG_TRY(upload_vec(y.o.b, p[7], D));
+        RG_TRY(upload_vec(y.ln1g, p[8], D));
+        RG_TRY(upload_vec(y.ln1b, p[9], D));
+        RG_TRY(upload_matrix(m, y.fc1.W, y.fc1.ldw, 0, p[10], D, F));
+        RG_TRY(upload_vec(y.fc1.b, p[11], F));
+        RG_TRY(upload_matrix(m, y.fc2.W, y.fc2.ldw, 0, p[12], F, D));
+        RG_TRY(upload_vec(y.fc2.b, p[13], D));
+        RG_TRY(upload_vec(y.ln2g, p[14], D));
+        RG_TRY(upload_vec(y.ln2b, p[15], D));
+    }
+    RG_TRY(upload_vec(m->lnfg, data[n - 4], D));
+    RG_TRY(upload_vec(m->lnfb, data[n - 3], D));
+    RG_TRY(upload_matrix(m, m->head.W, m->head.ldw, 0, data[n - 2], D, V));
+    RG_TRY(upload_vec(m->head.b, data[n - 1], V));
+    m->loaded = true;
+    m->pos = 0;
+    m->curB = 0;
+    return RG_OK;
+}
+
+// ---------------------------------------------------------------------------
+// prompt pass / full forward
+// ---------------------------------------------------------------------------
+static rg_status ensure_rows(rg_gpt* m, size_t rows) {
+    if (rows <= m->rowsCap) return RG_OK;
+    RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    dfree(m, m->px), dfree(m, m->pln), dfree(m, m->pqkv), dfree(m, m->pattn), dfree(m, m->ph), dfree(m, m->plast);
+    m->px = m->pln = m->pqkv = m->pattn = m->ph = m->plast = nullptr;
+    m->rowsCap = 0;
+    RG_TRY(dalloc(m, (void**)&m->px, rows * m->D * 4));
+    RG_TRY(dalloc(m, (void**)&m->pln, rows * m->D * 4));
+    RG_TRY(dalloc(m, (void**)&m->pqkv, rows * 3 * m->D * 4));
+    RG_TRY(dalloc(m, (void**)&m->pattn, rows * m->D * 4));
+    RG_TRY(dalloc(m, (void**)&m->ph, rows * m->F * 4));
+    RG_TRY(dalloc(m, (void**)&m->plast, (size_t)m->Bmax * m->D * 4));
+    m->rowsCap = rows;
+    return RG_OK;
+}
+
+static rg_status gemm(rg_gpt* m, const float* A, int M, const rg_linear& lin, float* Cout, const float* res, int act) {
+    rg_gemm_args p;
+    memset(&p, 0, sizeof(p));
+    p.A = A, p.lda = lin.K;
+    p.W = lin.W, p.ldw = lin.ldw;
+    p.C = Cout, p.ldc = lin.N;
+    p.M = M, p.N = lin.N, p.K = lin.K;
+    p.bias = lin.b, p.res = res, p.ldres = lin.N, p.act = act;
+    if (m->bf16) RG_CUDA(rg_gemm_launch<__nv_bfloat16>(m->ctx->stream, p, 1));
+    else RG_CUDA(rg_gemm_launch<float>(m->ctx->stream, p, 1));
+    RG_LAUNCHED(m->ctx);
+    return RG_OK;
+}
+
+template <typename KT>
+static rg_status attn_rows(rg_gpt* m, int l, int B, int T) {
+    const KT* kc = (const KT*)(m->kc + (size_t)l * m->kv_layer_bytes);
+    const KT* vc = (const KT*)(m->vc + (size_t)l * m->kv_layer_bytes);
+    cudaStream_t s = m->ctx->stream;
+    rg_kv_scatter_kernel<KT><<<B * T, 256, 0, s>>>(m->pqkv, (KT*)kc, (KT*)vc, T, m->H, m->hd, m->C, m->D);
+    dim3 grid(rg_cdiv(T, 8), m->H, B);
+    const float scale = 1.f / sqrtf((float)m->hd);
+    const int causal = m->cfg.causal ? 1 : 0;
+    if (m->hd == 32)
+        rg_attn_rows_kernel<KT, 32><<<grid, 256, 0, s>>>(m->pqkv, kc, vc, m->pattn, T, m->H, m->C, m->D, scale, causal);
+    else if (m->hd == 64)
+        rg_attn_rows_kernel<KT, 64><<<grid, 256, 0, s>>>(m->pqkv, kc, vc, m->pattn, T, m->H, m->C, m->D, scale, causal);
+    else
+        rg_attn_rows_kernel<KT, 128><<<grid, 256, 0, s>>>(m->pqkv, kc, vc, m->pattn, T, m->H, m->C, m->D, scale, causal);
+    m->ctx->launches += 2;
+    RG_CUDA(cudaGetLastError());
+    return RG_OK;
+}
+
+// Runs ids tokens[b][0..T) (already on the device) through the model.  With
+// full != null writes logits of every row there ([B*T][V], device); otherwise
+// computes the last row only into m->logits and its greedy pick into
+// m->picks / tokens[b][T].
+static rg_status run_rows(rg_gpt* m, int B, int T, float* full) {
+    const int M = B * T, D = m->D;
+    RG_TRY(ensure_rows(m, (size_t)M));
+    cudaStream_t s = m->ctx->stream;
+    if (m->bf16)
+        rg_embed_rows_kernel<__nv_bfloat16><<<M, 128, 0, s>>>(m->tokens, m->C, T, (const __nv_bfloat16*)m->wte,
+                                                              (const __nv_bfloat16*)m->wpe, D, m->ldt, m->px);
+    else
+        rg_embed_rows_kernel<float><<<M, 128, 0, s>>>(m->tokens, m->C, T, (const float*)m->wte, (const float*)m->wpe, D,
+                                                      m->ldt, m->px);
+    RG_LAUNCHED(m->ctx);
+    const int act = m->cfg.activation;
+    for (int l = 0; l < m->L; l++) {
+        rg_layer& y = m->layers[l];
+        rg_ln_rows_kernel<<<rg_cdiv(M, 8), 256, 0, s>>>(m->px, D, y.ln1g, y.ln1b, m->pln, (size_t)M, D, 1e-5f);
+        RG_LAUNCHED(m->ctx);
+        RG_TRY(gemm(m, m->pln, M, y.qkv, m->pqkv, nullptr, -1));
+        if (m->bf16) RG_TRY(attn_rows<__nv_bfloat16>(m, l, B, T));
+        else RG_TRY(attn_rows<float>(m, l, B, T));
+        RG_TRY(gemm(m, m->pattn, M, y.o, m->px, m->px, -1));
+        rg_ln_rows_kernel<<<rg_cdiv(M, 8), 256, 0, s>>>(m->px, D, y.ln2g, y.ln2b, m->pln, (size_t)M, D, 1e-5f);
+        RG_LAUNCHED(m->ctx);
+        RG_TRY(gemm(m, m->pln, M, y.fc1, m->ph, nullptr, act));
+        RG_TRY(gemm(m, m->ph, M, y.fc2, m->px, m->px, -1));
+    }
+    if (full) {
+        rg_ln_rows_kernel<<<rg_cdiv(M, 8), 256, 0, s>>>(m->px, D, m->lnfg, m->lnfb, m->pln, (size_t)M, D, 1e-5f);
+        RG_LAUNCHED(m->ctx);
+        RG_TRY(gemm(m, m->pln, M, m->head, full, nullptr, -1));
+    } else {
+        rg_ln_rows_kernel<<<rg_cdiv(B, 8), 256, 0, s>>>(m->px + (size_t)(T - 1) * D, (long long)T * D, m->lnfg, m->lnfb,
+                                                        m->plast, (size_t)B, D, 1e-5f);
+        RG_LAUNCHED(m->ctx);
+        RG_TRY(gemm(m, m->plast, B, m->head, m->logits, nullptr, -1));
+        rg_argmax_rows_kernel<<<B, 1024, 0, s>>>(m->logits, m->V, m->picks, m->tokens, m->C, T);
+        RG_LAUNCHED(m->ctx);
+    }
+    RG_CUDA(cudaGetLastError());
+    return RG_OK;
+}
+
+static rg_status check_ready(rg_gpt* m, size_t B) {
+    if (!m->loaded) return rg_fail(RG_ERR_INVALID_INPUT, "model parameters have not been loaded");
+    if (B == 0 || B > (size_t)m->Bmax)
+        return rg_fail(RG_ERR_INVALID_INPUT, "batch %zu outside 1..max_batch (%d)", B, m->Bmax);
+    return RG_OK;
+}
+
+// ids [B][T] host -> tokens[b][0..T)
+static rg_status upload_ids(rg_gpt* m, const uint32_t* ids, size_t B, size_t T) {
+    for (size_t i = 0; i < B * T; i++)
+        if (ids[i] >= (uint32_t)m->V)
+            return rg_fail(RG_ERR_INVALID_INPUT, "Invalid input: index %u out of bounds for vocabulary size %d", ids[i], m->V);
+    RG_CUDA(cudaMemcpy2DAsync(m->tokens, (size_t)m->C * 4, ids, T * 4, T * 4, B, cudaMemcpyHostToDevice, m->ctx->stream));
+    return RG_OK;
+}
+
+extern "C" rg_status rg_gpt_forward(rg_gpt* m, const float* idx_f32, size_t B, size_t T, float* logits) {
+    if (!m || !idx_f32 || !logits) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    RG_TRY(check_ready(m, B));
+    if (T == 0) return rg_fail(RG_ERR_INVALID_INPUT, "empty sequence");
+    if (T > (size_t)m->C)
+        return rg_fail(RG_ERR_INVALID_INPUT, "Invalid input: index %zu out of bounds for vocabulary size %d (positions)", T - 1,
+                       m->C);
+    std::vector<uint32_t> ids(B * T);
+    for (size_t i = 0; i < B * T; i++) {
+        const float f = idx_f32[i];
+        if (!(f >= 0.f) || (size_t)f >= (size_t)m->V)
+            return rg_fail(RG_ERR_INVALID_INPUT, "Invalid input: index %g out of bounds for vocabulary size %d", (double)f, m->V);
+        ids[i] = (uint32_t)f;  // `as usize` truncation, src/ops/embedding.rs:50
+    }
+    rg_ctx_guard g(m->ctx);
+    RG_TRY(upload_ids(m, ids.data(), B, T));
+    const size_t need = B * T * (size_t)m->V;
+    if (need > m->plogitsCap) {
+        RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+        dfree(m, m->plogits);
+        m->plogits = nullptr, m->plogitsCap = 0;
+        RG_TRY(dalloc(m, (void**)&m->plogits, need * 4));
+        m->plogitsCap = need;
+    }
+    RG_TRY(run_rows(m, (int)B, (int)T, m->plogits));
+    RG_CUDA(cudaMemcpyAsync(logits, m->plogits, need * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+    RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    m->pos = 0, m->curB = 0;  // the cache now holds this call's keys, not a generation context
+    return RG_OK;
+}
+
+static rg_status set_pos(rg_gpt* m, size_t T) {
+    rg_set_int2_kernel<<<1, 1, 0, m->ctx->stream>>>(m->d_pos_next, m->d_pos, (int)T);
+    RG_LAUNCHED(m->ctx);
+    RG_CUDA(cudaGetLastError());
+    m->pos = T;
+    return RG_OK;
+}
+
+static rg_status prefill_locked(rg_gpt* m, const uint32_t* ids, size_t B, size_t T, float* logits_last, uint32_t* argmax) {
+    if (T == 0) return rg_fail(RG_ERR_INVALID_INPUT, "empty prompt");
+    if (T > (size_t)m->C) return rg_fail(RG_ERR_INVALID_INPUT, "prompt of %zu ids exceeds block_size %d", T, m->C);
+    RG_TRY(upload_ids(m, ids, B, T));
+    RG_TRY(run_rows(m, (int)B, (int)T, nullptr));
+    RG_TRY(set_pos(m, T));
+    m->curB = B;
+    if (logits_last)
+        RG_CUDA(cudaMemcpyAsync(logits_last, m->logits, B * (size_t)m->V * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+    if (argmax) RG_CUDA(cudaMemcpyAsync(argmax, m->picks, B * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+    if (logits_last || argmax) RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    return RG_OK;
+}
+
+extern "C" rg_status rg_gpt_prefill(rg_gpt* m, const uint32_t* ids, size_t B, size_t T, float* logits_last,
+                                    uint32_t* argmax) {
+    if (!m || !ids) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    RG_TRY(check_ready(m, B));
+    rg_ctx_guard g(m->ctx);
+    return prefill_locked(m, ids, B, T, logits_last, argmax);
+}
+
+// ---------------------------------------------------------------------------
+// token step
+// ---------------------------------------------------------------------------
+template <typename WT, int BT>
+static void launch_gemv_bt(rg_gpt* m, const rg_gemv_args& a) {
+    constexpr int NT = 32 * rg_wvec<WT>::N;
+    dim3 grid(rg_cdiv(a.N, NT), a.ksplit, rg_cdiv(a.B, BT));
+    const int xlen = a.in.post == RG_POST_LN ? a.K : a.krows;
+    const size_t smem = (size_t)BT * xlen * 4;
+    rg_gemv_kernel<WT, BT><<<grid, 256, smem, m->ctx->stream>>>(a);
+}
+template <typename WT>
+static void launch_gemv_wt(rg_gpt* m, const rg_gemv_args& a) {
+    switch (batch_tile(a.B)) {
+        case 1: launch_gemv_bt<WT, 1>(m, a); break;
+        case 2: launch_gemv_bt<WT, 2>(m, a); break;
+        case 4: launch_gemv_bt<WT, 4>(m, a); break;
+        default: launch_gemv_bt<WT, 8>(m, a); break;
+    }
+}
+static void launch_gemv(rg_gpt* m, const rg_linear& lin, const rg_vec_in& in, int B) {
+    rg_gemv_args a;
+    a.in = in;
+    a.W = lin.W, a.ldw = lin.ldw, a.K = lin.K, a.N = lin.N, a.B = B;
+    a.ksplit = lin.ksplit, a.krows = lin.krows, a.out = lin.parts;
+    if (m->bf16) launch_gemv_wt<__nv_bfloat16>(m, a);
+    else launch_gemv_wt<float>(m, a);
+}
+
+static rg_vec_in vec_reduce(const float* base, const float* bias, const rg_linear* producer, int post) {
+    rg_vec_in in;
+    memset(&in, 0, sizeof(in));
+    in.kind = RG_IN_REDUCE;
+    in.base = base, in.bias = bias;
+    in.parts = producer ? producer->parts : nullptr;
+    in.nparts = producer ? producer->ksplit : 0;
+    in.post = post;
+    return in;
+}
+
+template <typename KT>
+static void launch_attn_step(rg_gpt* m, int l, int B) {
+    rg_layer& y = m->layers[l];
+    rg_attn_step_args a;
+    a.qkv_parts = y.qkv.parts, a.nparts = y.qkv.ksplit, a.qkv_bias = y.qkv.b;
+    a.kcache = m->kc + (size_t)l * m->kv_layer_bytes, a.vcache = m->vc + (size_t)l * m->kv_layer_bytes;
+    a.ap = m->ap, a.pos = m->d_pos;
+    a.B = B, a.H = m->H, a.C = m->C, a.D = m->D, a.NS = m->NS;
+    a.scale = 1.f / sqrtf((float)m->hd);
+    dim3 grid(m->NS, m->H, B);
+    cudaStream_t s = m->ctx->stream;
+    if (m->hd == 32) rg_attn_step_kernel<KT, 32><<<grid, 128, 0, s>>>(a);
+    else if (m->hd == 64) rg_attn_step_kernel<KT, 64><<<grid, 128, 0, s>>>(a);
+    else rg_attn_step_kernel<KT, 128><<<grid, 128, 0, s>>>(a);
+}
+
+// Enqueue the kernels of one token step for B sequences; returns how many.
+static int enqueue_step(rg_gpt* m, int B) {
+    cudaStream_t s = m->ctx->stream;
+    int n = 0;
+    if (m->bf16)
+        rg_embed_step_kernel<__nv_bfloat16><<<B, 128, 0, s>>>(m->tokens, m->C, (const __nv_bfloat16*)m->wte,
+                                                              (const __nv_bfloat16*)m->wpe, m->D, m->ldt, m->xa,
+                                                              m->d_pos_next, m->d_pos);
+    else
+        rg_embed_step_kernel<float><<<B, 128, 0, s>>>(m->tokens, m->C, (const float*)m->wte, (const float*)m->wpe, m->D,
+                                                      m->ldt, m->xa, m->d_pos_next, m->d_pos);
+    n++;
+    const int act_post = m->cfg.activation == RG_ACT_RELU ? RG_POST_RELU : RG_POST_GELU;
+    for (int l = 0; l < m->L; l++) {
+        rg_layer& y = m->layers[l];
+        const rg_layer* prev = l ? &m->layers[l - 1] : nullptr;
+        // x = x + b2 + fc2 partials of the previous block; LN1; QKV
+        rg_vec_in in = vec_reduce(m->xa, prev ? prev->fc2.b : nullptr, prev ? &prev->fc2 : nullptr, RG_POST_LN);
+        in.gamma = y.ln1g, in.beta = y.ln1b, in.store = m->xb;
+        launch_gemv(m, y.qkv, in, B);
+        if (m->bf16) launch_attn_step<__nv_bfloat16>(m, l, B);
+        else launch_attn_step<float>(m, l, B);
+        // merged heads -> output projection
+        rg_vec_in ia;
+        memset(&ia, 0, sizeof(ia));
+        ia.kind = RG_IN_ATTN, ia.ap = m->ap, ia.H = m->H, ia.hd = m->hd, ia.NS = m->NS, ia.post = RG_POST_NONE;
+        launch_gemv(m, y.o, ia, B);
+        // x = x + bo + partials; LN2; FC1
+        rg_vec_in i1 = vec_reduce(m->xb, y.o.b, &y.o, RG_POST_LN);
+        i1.gamma = y.ln2g, i1.beta = y.ln2b, i1.store = m->xa;
+        launch_gemv(m, y.fc1, i1, B);
+        // act(b1 + partials); FC2
+        rg_vec_in i2 = vec_reduce(nullptr, y.fc1.b, &y.fc1, act_post);
+        launch_gemv(m, y.fc2, i2, B);
+        n += 5;
+    }
+    const rg_layer& last = m->layers[m->L - 1];
+    rg_vec_in ih = vec_reduce(m->xa, last.fc2.b, &last.fc2, RG_POST_LN);
+    ih.gamma = m->lnfg, ih.beta = m->lnfb, ih.store = nullptr;
+    launch_gemv(m, m->head, ih, B);
+    rg_pick_args pa;
+    pa.parts = m->head.parts, pa.nparts = m->head.ksplit, pa.bias = m->head.b, pa.logits = m->logits;
+    pa.tokens = m->tokens, pa.picks = m->picks, pa.pos = m->d_pos, pa.pos_next = m->d_pos_next;
+    pa.B = B, pa.V = m->V, pa.C = m->C;
+    rg_pick_kernel<<<B, 1024, 0, s>>>(pa);
+    n += 2;
+    return n;
+}
+
+static rg_status step_ready(rg_gpt* m, size_t steps) {
+    if (!m->cfg.causal)
+        return rg_fail(RG_ERR_UNSUPPORTED,
+                       "the KV-cache token step needs causal attention; this model uses the reference's unmasked attention");
+    if (m->curB == 0) return rg_fail(RG_ERR_INVALID_INPUT, "no context: call rg_gpt_prefill first");
+    if (m->pos + steps > (size_t)m->C)
+        return rg_fail(RG_ERR_CONTEXT_FULL, "context full: position %zu + %zu steps exceeds block_size %d", m->pos, steps, m->C);
+    return RG_OK;
+}
+
+static rg_status run_steps(rg_gpt* m, size_t steps) {
+    const int B = (int)m->curB;
+    cudaStream_t s = m->ctx->stream;
+    if (!m->use_graph) {
+        for (size_t i = 0; i < steps; i++) {
+            m->ctx->launches += enqueue_step(m, B);
+            RG_CUDA(cudaGetLastError());
+        }
+    } else {
+        if (!m->graph || m->graphB != (size_t)B) {
+            if (m->graph) cudaGraphExecDestroy(m->graph), m->graph = nullptr;
+            cudaGraph_t gr = nullptr;
+            RG_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+            m->kernels_per_step = enqueue_step(m, B);
+            cudaError_t e = cudaStreamEndCapture(s, &gr);
+            if (e != cudaSuccess) return rg_fail(RG_ERR_BACKEND, "graph capture failed: %s", cudaGetErrorString(e));
+            e = cudaGraphInstantiate(&m->graph, gr, 0);
+            cudaGraphDestroy(gr);
+            if (e != cudaSuccess) return rg_fail(RG_ERR_BACKEND, "graph instantiate failed: %s", cudaGetErrorString(e));
+            m->graphB = B;
+        }
+        for (size_t i = 0; i < steps; i++) RG_CUDA(cudaGraphLaunch(m->graph, s));
+        m->ctx->launches += (uint64_t)m->kernels_per_step * steps;
+    }
+    m->pos += steps;
+    return RG_OK;
+}
+
+extern "C" rg_status rg_gpt_decode_step(rg_gpt* m, const uint32_t* tok, float* logits, uint32_t* argmax) {
+    if (!m || !tok) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    rg_ctx_guard g(m->ctx);
+    RG_TRY(step_ready(m, 1));
+    const size_t B = m->curB;
+    for (size_t b = 0; b < B; b++)
+        if (tok[b] >= (uint32_t)m->V)
+            return rg_fail(RG_ERR_INVALID_INPUT, "Invalid input: index %u out of bounds for vocabulary size %d", tok[b], m->V);
+    RG_CUDA(cudaMemcpy2DAsync(m->tokens + m->pos, (size_t)m->C * 4, tok, 4, 4, B, cudaMemcpyHostToDevice, m->ctx->stream));
+    RG_TRY(run_steps(m, 1));
+    if (logits) RG_CUDA(cudaMemcpyAsync(logits, m->logits, B * (size_t)m->V * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+    if (argmax) RG_CUDA(cudaMemcpyAsync(argmax, m->picks, B * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+    RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    return RG_OK;
+}
+
+extern "C" rg_status rg_gpt_decode_run(rg_gpt* m, size_t n_steps) {
+    if (!m) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    rg_ctx_guard g(m->ctx);
+    RG_TRY(step_ready(m, n_steps));
+    return run_steps(m, n_steps);
+}
+
+extern "C" rg_status rg_gpt_rewind(rg_gpt* m, size_t T, const uint32_t* tok) {
+    if (!m) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    rg_ctx_guard g(m->ctx);
+    if (m->curB == 0) return rg_fail(RG_ERR_INVALID_INPUT, "no context: call rg_gpt_prefill first");
+    if (T > m->pos) return rg_fail(RG_ERR_INVALID_INPUT, "cannot rewind forward: position %zu, asked for %zu", m->pos, T);
+    if (T >= (size_t)m->C) return rg_fail(RG_ERR_CONTEXT_FULL, "position %zu is outside block_size %d", T, m->C);
+    if (tok) {
+        for (size_t b = 0; b < m->curB; b++)
+            if (tok[b] >= (uint32_t)m->V) return rg_fail(RG_ERR_INVALID_INPUT, "Invalid input: index %u out of bounds", tok[b]);
+        RG_CUDA(cudaMemcpy2DAsync(m->tokens + T, (size_t)m->C * 4, tok, 4, 4, m->curB, cudaMemcpyHostToDevice,
+                                  m->ctx->stream));
+    }
+    return set_pos(m, T);
+}
+
+extern "C" rg_status rg_gpt_read_tokens(rg_gpt* m, size_t from, size_t n, uint32_t* out) {
+    if (!m || !out) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    rg_ctx_guard g(m->ctx);
+    if (m->curB == 0) return rg_fail(RG_ERR_INVALID_INPUT, "no context");
+    if (from + n > (size_t)m->C) return rg_fail(RG_ERR_INVALID_INPUT, "ids [%zu, %zu) outside block_size %d", from, from + n, m->C);
+    if (n)
+        RG_CUDA(cudaMemcpy2DAsync(out, n * 4, m->tokens + from, (size_t)m->C * 4, n * 4, m->curB, cudaMemcpyDeviceToHost,
+                                  m->ctx->stream));
+    RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    return RG_OK;
+}
+
+extern "C" size_t rg_gpt_position(const rg_gpt* m) { return m ? m->pos : 0; }
+
+extern "C" rg_status rg_gpt_reset(rg_gpt* m) {
+    if (!m) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    rg_ctx_guard g(m->ctx);
+    m->curB = 0;
+    return set_pos(m, 0);
+}
+
+// ---------------------------------------------------------------------------
+// generate
+// ---------------------------------------------------------------------------
+extern "C" rg_status rg_gpt_generate(rg_gpt* m, const uint32_t* prompt, size_t B, size_t P, size_t max_new,
+                                     float temperature, size_t top_k, uint64_t seed, uint32_t* out) {
+    (void)temperature;
+    (void)seed;
+    if (!m || !prompt || (!out && max_new)) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    RG_TRY(check_ready(m, B));
+    if (top_k != 1)
+        return rg_fail(RG_ERR_UNSUPPORTED, "only greedy decoding (top_k = 1) is implemented; got top_k = %zu", top_k);
+    if (P == 0) return rg_fail(RG_ERR_INVALID_INPUT, "empty prompt");
+    if (max_new == 0) return RG_OK;
+    rg_ctx_guard g(m->ctx);
+    if (m->cfg.causal) {
+        if (P + max_new - 1 > (size_t)m->C)
+            return rg_fail(RG_ERR_CONTEXT_FULL,
+                           "prompt %zu + %zu new ids needs %zu cache rows, block_size is %d (the KV cache cannot slide)", P,
+                           max_new, P + max_new - 1, m->C);
+        RG_TRY(prefill_locked(m, prompt, B, P, nullptr, nullptr));
+        if (max_new > 1) RG_TRY(run_steps(m, max_new - 1));
+        if (P + max_new <= (size_t)m->C) {
+            RG_CUDA(cudaMemcpy2DAsync(out, max_new * 4, m->tokens + P, (size_t)m->C * 4, max_new * 4, B,
+                                      cudaMemcpyDeviceToHost, m->ctx->stream));
+        } else {  // the last pick has no slot in the id buffer: it is in picks
+            if (max_new > 1)
+                RG_CUDA(cudaMemcpy2DAsync(out, max_new * 4, m->tokens + P, (size_t)m->C * 4, (max_new - 1) * 4, B,
+                                          cudaMemcpyDeviceToHost, m->ctx->stream));
+            RG_CUDA(cudaMemcpy2DAsync(out + (max_new - 1), max_new * 4, m->picks, 4, 4, B, cudaMemcpyDeviceToHost,
+                                      m->ctx->stream));
+        }
+        RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+        return RG_OK;
+    }
+    // The reference's loop proper (no mask, so no cache): every new id re-runs the
+    // whole window of the last block_size ids (wasm_api.rs:102-118).
+    std::vector<std::vector<uint32_t>> ids(B);
+    for (size_t b = 0; b < B; b++) ids[b].assign(prompt + b * P, prompt + (b + 1) * P);
+    std::vector<uint32_t> window, picks(B);
+    for (size_t i = 0; i < max_new; i++) {
+        const size_t len = ids[0].size();
+        const size_t T = std::min(len, (size_t)m->C), start = len - T;
+        window.resize(B * T);
+        for (size_t b = 0; b < B; b++) memcpy(&window[b * T], &ids[b][start], T * 4);
+        RG_TRY(upload_ids(m, window.data(), B, T));
+        RG_TRY(run_rows(m, (int)B, (int)T, nullptr));
+        RG_CUDA(cudaMemcpyAsync(picks.data(), m->picks, B * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+        RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+        for (size_t b = 0; b < B; b++) {
+            ids[b].push_back(picks[b]);
+            out[b * max_new + i] = picks[b];
+        }
+    }
+    m->pos = 0, m->curB = 0;
+    return RG_OK;
+}
+
+extern "C" double rg_gpt_decode_step_bytes(const rg_gpt* m, size_t B, double mean_ctx) {
+    if (!m) return 0.0;
+    const double D = m->D, V = m->V, L = m->L;
+    const double w = L * (12.0 * D * D + 13.0 * D) + D * V + V + 4.0 * D;
+    const double kv = m->bf16 ? 2.0 : 4.0;
+    return (double)m->wsize * w + (double)B * kv * 2.0 * L * D * mean_ctx;
+}

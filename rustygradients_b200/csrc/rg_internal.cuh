@@ -1,0 +1,151 @@
+// Shared internals of the B200 GPT token-loop library: handle structs, error
+// plumbing and small device helpers.  Not part of the public ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdarg.h>
+#include <stdio.h>
+
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/rg_b200.h"
+
+// ---------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------
+rg_status rg_fail(rg_status st, const char* fmt, ...);
+void rg_clear_error();
+
+#define RG_CUDA(expr)                                                                       \
+    do {                                                                                    \
+        cudaError_t _e = (expr);                                                            \
+        if (_e != cudaSuccess)                                                              \
+            return rg_fail(RG_ERR_BACKEND, "CUDA error %d (%s) at %s:%d: %s", (int)_e,      \
+                           cudaGetErrorName(_e), __FILE__, __LINE__, cudaGetErrorString(_e)); \
+    } while (0)
+
+#define RG_TRY(expr)                  \
+    do {                              \
+        rg_status _s = (expr);        \
+        if (_s != RG_OK) return _s;   \
+    } while (0)
+
+// ---------------------------------------------------------------------------
+// handles
+// ---------------------------------------------------------------------------
+struct rg_ctx {
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    std::mutex mu;
+    uint64_t launches = 0;
+    int* d_flag = nullptr;  // device word kernels raise on invalid input
+    int* h_flag = nullptr;  // pinned mirror
+};
+
+struct rg_devbuf {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    int device = 0;
+    ~rg_devbuf();
+};
+
+struct rg_storage {
+    rg_ctx* ctx = nullptr;
+    std::shared_ptr<rg_devbuf> buf;  // reshape views alias the same buffer
+    std::vector<size_t> shape;
+    size_t len = 0;
+    const float* data() const { return static_cast<const float*>(buf->ptr); }
+    float* data() { return static_cast<float*>(buf->ptr); }
+};
+
+rg_status rg_alloc_storage(rg_ctx* ctx, const size_t* shape, int ndim, rg_storage** out);
+
+struct rg_ctx_guard {
+    rg_ctx* c;
+    explicit rg_ctx_guard(rg_ctx* ctx) : c(ctx) {
+        c->mu.lock();
+        cudaSetDevice(c->device);
+    }
+    ~rg_ctx_guard() { c->mu.unlock(); }
+};
+
+#define RG_LAUNCHED(ctx) ((ctx)->launches++)
+
+static inline int rg_cdiv(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// ---------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+#define RG_FULL_MASK 0xffffffffu
+
+__device__ __forceinline__ float rg_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(RG_FULL_MASK, v, o);
+    return v;
+}
+__device__ __forceinline__ float rg_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(RG_FULL_MASK, v, o));
+    return v;
+}
+
+// Welford triple (count, mean, M2) and Chan's pairwise merge: the one-pass
+// statistics of fused::layer_norm_fused (src/backend/fused.rs:22-144).
+struct rg_welford {
+    float n, mean, m2;
+};
+__device__ __forceinline__ void rg_welford_add(rg_welford& w, float x) {
+    w.n += 1.f;
+    float d = x - w.mean;
+    w.mean += d / w.n;
+    w.m2 += d * (x - w.mean);
+}
+__device__ __forceinline__ rg_welford rg_welford_merge(rg_welford a, rg_welford b) {
+    rg_welford r;
+    r.n = a.n + b.n;
+    if (r.n == 0.f) {
+        r.mean = 0.f;
+        r.m2 = 0.f;
+        return r;
+    }
+    float d = b.mean - a.mean;
+    float f = b.n / r.n;
+    r.mean = a.mean + d * f;
+    r.m2 = a.m2 + b.m2 + d * d * a.n * f;
+    return r;
+}
+__device__ __forceinline__ rg_welford rg_welford_warp(rg_welford w) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        rg_welford t;
+        t.n = __shfl_xor_sync(RG_FULL_MASK, w.n, o);
+        t.mean = __shfl_xor_sync(RG_FULL_MASK, w.mean, o);
+        t.m2 = __shfl_xor_sync(RG_FULL_MASK, w.m2, o);
+        w = rg_welford_merge(w, t);
+    }
+    return w;
+}
+
+// tanh-GELU with the reference's constants (src/backend/fused.rs:152-163,
+// src/backend/cuda_kernels.cu:120-131).
+__device__ __forceinline__ float rg_gelu_tanh(float x) {
+    const float c0 = 0.7978845608f, c1 = 0.044715f;
+    float inner = c0 * (x + c1 * x * x * x);
+    return 0.5f * x * (1.f + tanhf(inner));
+}
+__device__ __forceinline__ float rg_apply_act(float x, int act) {
+    return act == RG_ACT_RELU ? fmaxf(x, 0.f) : rg_gelu_tanh(x);
+}
+
+__device__ __forceinline__ float rg_to_float(float v) { return v; }
+__device__ __forceinline__ float rg_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+#endif  // __CUDACC__
