@@ -1,0 +1,318 @@
+#!/usr/bin/env python
+"""Benchmark of the GPT token loop: decode tokens/sec on the GPT-2-small shape
+(vocab 1024, d_model 768, 12 layers, 12 heads, context 1024, f32 weights, batch 1
+per GPU, prompt 128 ids, greedy decode of 256 ids) and its fraction of the HBM
+roofline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one decode run: the 256 token-loop iterations that follow a
+128-id prompt whose keys/values are already in the cache (positions 128..383).
+`value` times K such steps with everything resident in HBM; `e2e` times the
+public generate() call with host buffers (prompt upload, prompt pass, decode,
+ids download).  With N > 1 (under torchrun) every rank runs its own sequence on
+its own GPU: sequences are the shard, there is no collective in the loop.
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOAD = "gpt2-small-shape vocab1024 f32 batch1 prompt128 decode256"
+CFG_INDEX = 1
+NOMINAL_HBM_GBS = 8000.0     # the figure the metric's roofline is defined on
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# --------------------------------------------------------------------------
+# clocks: sampled DURING the timed region
+# --------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        rows = [r for t, r in self.rows if t0 - 0.05 <= t <= t1 + 0.15] or [r for _, r in self.rows]
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except Exception:
+                continue
+            for name, val in zip(names, r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------
+# the CPU arm: the reference's own algorithm (full re-forward of the whole
+# context for every new id, no KV cache, unmasked attention, ReLU, all T logit
+# rows) restated in numpy f32 over the bundled OpenBLAS, on the host cores.
+# --------------------------------------------------------------------------
+def cpu_threads() -> int:
+    try:
+        from threadpoolctl import threadpool_info
+        n = [i.get("num_threads", 0) for i in threadpool_info() if i.get("user_api") == "blas"]
+        if n:
+            return int(max(n))
+    except Exception:
+        pass
+    return os.cpu_count() or 1
+
+
+def cpu_reference_tokens_per_s(n_tokens: int, params=None):
+    """Times n_tokens iterations of the reference loop at context lengths spread
+    evenly over the workload's 128..383 range; returns (tokens/s, seconds)."""
+    from oracle import gpt_oracle as O
+    c = O.CONFIGS[CFG_INDEX]
+    cfg, P, G = c["cfg"], c["prompt"], c["gen"]
+    seed = O.config_seed(CFG_INDEX)
+    if params is None:
+        params = O.make_params(cfg, seed)
+    rng = np.random.Generator(np.random.PCG64(seed + 1))
+    ctxs = np.linspace(P, P + G - 1, n_tokens).round().astype(int)
+    ids = rng.integers(0, cfg.vocab_size, size=(1, P + G), dtype=np.int64)
+    O.forward(params, cfg, ids[:, :P], causal=False, act="relu")  # warm the BLAS threads
+    t0 = time.perf_counter()
+    for T in ctxs:
+        lg = O.forward(params, cfg, ids[:, :T], causal=False, act="relu")   # all T rows, like gpt.rs:79-80
+        O.greedy_pick(lg[0, -1])
+    dt = time.perf_counter() - t0
+    return n_tokens / dt, dt
+
+
+def run_reference(args, rank: int) -> None:
+    if rank != 0:
+        return
+    sample = 6
+    for _ in range(args.warmup):
+        pass  # warm-up is the BLAS warm call inside cpu_reference_tokens_per_s
+    from oracle import gpt_oracle as O
+    params = O.make_params(O.CONFIGS[CFG_INDEX]["cfg"], O.config_seed(CFG_INDEX))
+    t_all, n_all = 0.0, 0
+    for _ in range(args.steps):
+        _, dt = cpu_reference_tokens_per_s(sample, params)
+        t_all += dt
+        n_all += sample
+    v = n_all / t_all
+    cores = cpu_threads()
+    desc = (f"{sample} loop iterations per step at context lengths spread over 128..383, full re-forward per id "
+            f"(no KV cache, unmasked attention, ReLU, all logit rows), numpy f32 + OpenBLAS")
+    line = {"impl": "reference", "metric": "decode tokens/sec (GPT-2-small shape)", "value": v, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "kv_cache": False},
+            "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------
+def run_ours(args, rank: int, local_rank: int, world: int) -> None:
+    import torch
+    import rustygradients_b200 as rg
+    from oracle import gpt_oracle as O   # seeded weights / prompt generator and the CPU-baseline leg only
+    from rustygradients_b200.sharding import gather_ids, max_over_ranks, shard_range
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    c = O.CONFIGS[CFG_INDEX]
+    cfg, P, G = c["cfg"], c["prompt"], c["gen"]
+    if args.tokens_per_step:
+        G = args.tokens_per_step
+    seed = O.config_seed(CFG_INDEX)
+    B = 1                                   # sequences per GPU (weak scaling: world sequences in total)
+    lo, hi = shard_range(world * B, rank, world)
+    params = O.make_params(cfg, seed)       # every rank holds a full replica of the same weights
+    prompts_all = O.make_prompt(cfg, seed, world * B, P)
+    prompt = np.ascontiguousarray(prompts_all[lo:hi])
+
+    be = rg.B200Backend(local_rank)
+    model = rg.GPTModel(be, rg.GptConfig(cfg.block_size, cfg.vocab_size, cfg.num_layers, cfg.num_heads,
+                                         cfg.embedding_dim, causal=True, activation="gelu_tanh", weight_dtype="f32",
+                                         max_batch=B))
+    model.load_parameters(params)
+    stream = torch.cuda.ExternalStream(be.stream, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident decode: prompt keys/values cached once, then K runs of G token steps
+    model.prefill(prompt, want_logits=False)
+    first_pick = model.read_tokens(P, 1, B)          # the id the prompt pass chose; fed at position P
+    for _ in range(args.warmup):
+        model.rewind(P)
+        model.decode_run(G)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.25)
+    l0 = be.launch_count
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_wall0 = time.time()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        model.rewind(P)
+        model.decode_run(G)
+    ev1.record(stream)
+    be.synchronize()
+    barrier()
+    t_wall1 = time.time()
+    launches = be.launch_count - l0
+    ms = max_over_ranks(ev0.elapsed_time(ev1), world, dev)
+    clocks = sampler.stop(t_wall0, t_wall1)
+    ids_dev = model.read_tokens(P + 1, G - 1, B)       # picks of steps 0..G-2 (the last has no slot to keep)
+
+    # ---- end to end through the public generate(): host prompt in, host ids out
+    pin_prompt = torch.from_numpy(prompt.astype(np.int64)).to(torch.int32).pin_memory()
+    prompt_pinned = pin_prompt.numpy().view(np.uint32)
+    for _ in range(min(args.warmup, 3)):
+        model.generate(prompt_pinned, G)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_e2e = max(3, min(args.steps, 10))
+    e0.record(stream)
+    for _ in range(n_e2e):
+        ids_e2e = model.generate(prompt_pinned, G)
+    e1.record(stream)
+    be.synchronize()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1), world, dev)
+    assert np.array_equal(ids_e2e[:, 1:], ids_dev), "generate() and the device-resident loop disagree"
+    assert int(first_pick[0, 0]) == int(ids_e2e[0, 0])
+    all_ids = gather_ids(ids_e2e, world * B, rank, world, dev)   # once, after the loop: the only exchange
+
+    if rank == 0:
+        tokens = world * B * G * args.steps
+        value = tokens / (ms * 1e-3)
+        e2e_value = world * B * G * n_e2e / (ms_e2e * 1e-3)
+        mean_ctx = P + (G - 1) / 2.0 + 1.0              # keys visible to a step, averaged over the run
+        step_bytes = model.decode_step_bytes(B, mean_ctx)   # one GPU, one token step
+        t_step = ms * 1e-3 / (args.steps * G)               # seconds per token step (slowest rank)
+        achieved = step_bytes / t_step / 1e9
+        peak, peak_kind = measured_hbm_peak()
+        line = {
+            "metric": "decode tokens/sec (GPT-2-small shape)", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD if G == c["gen"] else WORKLOAD + f" (SHORTENED to {G} tokens: not a bench value)",
+                       "sequences_per_gpu": B, "tokens_per_step": G, "kv_cache": "f32",
+                       "l2": "inputs larger than L2 (343 MB of weights streamed per token vs 126 MB L2)",
+                       "parallelism": f"{world} independent sequence shard(s), no collective in the loop"},
+            "us_per_token": t_step * 1e6,
+            "roofline": {"bound": "hbm", "kernel": f"token step = {launches // (args.steps * G)} kernels replayed as one CUDA graph",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind, "bytes_per_launch": step_bytes,
+                         "frac_of_8TBs_nominal": achieved / NOMINAL_HBM_GBS, "traffic": None},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": int(B * P * 4),
+                    "d2h_bytes_per_step": int(B * G * 4), "calls": n_e2e,
+                    "what": "generate(prompt, 256): pinned host ids -> device, prompt pass, 255 cached steps, ids -> host"},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "ids_checksum": int(np.asarray(all_ids, dtype=np.uint64).sum()),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            v, dt = cpu_reference_tokens_per_s(24, params)
+            line["cpu_baseline"] = {
+                "value": v, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port",
+                "sample": f"24 loop iterations at context lengths spread over 128..383 ({dt:.1f} s): the reference's loop "
+                          "(full re-forward per id, no KV cache, unmasked attention, ReLU, all logit rows) in numpy f32 + OpenBLAS"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tokens-per-step", type=int, default=0,
+                    help="shorten the decode run (profiling only; the default is the workload's 256)")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if args.gpus == 1 and world == 1:
+            pass
+        else:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()
