@@ -173,6 +173,22 @@ RG_API rg_status rg_gpt_reset(rg_gpt* m);
  * (weights + biases + LN + one table row pair + K/V of every cached position). */
 RG_API double rg_gpt_decode_step_bytes(const rg_gpt* m, size_t B, double mean_ctx);
 
+/* ---- allocation-free projection ------------------------------------------- */
+/* No counterpart in the reference.  y[N] = x[K] . W[K,N] + bias[N] (bias may be NULL)
+ * for a caller that cannot allocate device memory (inside a capture/replay region,
+ * a latency-critical loop, or a host that owns the whole device heap): all four
+ * pointers are DEVICE pointers the caller already owns, f32, W row-major and
+ * 16-byte aligned with N a multiple of 4.  The split-k partial sums live in a fixed
+ * 2 MiB array inside the library image (held by every GPU that loads the library
+ * until exit), which limits N to 16384 and K to 32768; larger sizes return
+ * RG_ERR_INVALID_INPUT.  Runs on the current device, on `stream` (a cudaStream_t).
+ * The first call on each device also looks up the array's address: make that
+ * call before any stream capture begins.  All calls share the array, so calls that
+ * overlap on the GPU race; nothing in it needs clearing between calls.  Never calls
+ * cudaMalloc / cudaFree or any allocating library routine. */
+RG_API rg_status rg_linear_row_noalloc(const float* x, const float* W, const float* bias, float* y, size_t K,
+                                       size_t N, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

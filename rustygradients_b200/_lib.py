@@ -117,6 +117,7 @@ SIGNATURES = {
     "rg_gpt_position": (C.c_size_t, [_P]),
     "rg_gpt_reset": (None, [_P]),
     "rg_gpt_decode_step_bytes": (C.c_double, [_P, _SZ, C.c_double]),
+    "rg_linear_row_noalloc": (None, [_P, _P, _P, _P, _SZ, _SZ, _P]),
 }
 
 _lib = None

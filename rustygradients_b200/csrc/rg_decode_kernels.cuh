@@ -379,7 +379,7 @@ struct rg_pick_args {
     int B, V, C;
 };
 
-__global__ void __launch_bounds__(1024) rg_pick_kernel(rg_pick_args p) {
+static __global__ void __launch_bounds__(1024) rg_pick_kernel(rg_pick_args p) {
     __shared__ float bv[32];
     __shared__ int bi[32];
     const int b = blockIdx.x, tid = threadIdx.x;
