@@ -173,6 +173,15 @@ RG_API rg_status rg_gpt_reset(rg_gpt* m);
  * (weights + biases + LN + one table row pair + K/V of every cached position). */
 RG_API double rg_gpt_decode_step_bytes(const rg_gpt* m, size_t B, double mean_ctx);
 
+/* Profiling aid of the persistent token-loop kernel (engine-only, nothing to mirror in the
+ * reference): when enabled, the last token step of every rg_gpt_decode_run records device
+ * timestamps per CTA and stage.  rg_gpt_trace_read returns rows of 10 uint64:
+ * cta, op index, stage (0 QKV, 1 attention, 2 out-proj, 3 FC1, 4 FC2, 5 LM head), layer,
+ * ns timestamps (stage start, input vector ready, dot products done, outputs stored), then SM
+ * cycles spent waiting for weight/KV chunks and for the input vector. */
+RG_API rg_status rg_gpt_trace_enable(rg_gpt* m, int on);
+RG_API rg_status rg_gpt_trace_read(rg_gpt* m, uint64_t* out, size_t cap_rows, size_t* n_rows);
+
 /* ---- allocation-free projection ------------------------------------------- */
 /* No counterpart in the reference.  y[N] = x[K] . W[K,N] + bias[N] (bias may be NULL)
  * for a caller that cannot allocate device memory (inside a capture/replay region,

@@ -117,6 +117,8 @@ SIGNATURES = {
     "rg_gpt_position": (C.c_size_t, [_P]),
     "rg_gpt_reset": (None, [_P]),
     "rg_gpt_decode_step_bytes": (C.c_double, [_P, _SZ, C.c_double]),
+    "rg_gpt_trace_enable": (None, [_P, C.c_int]),
+    "rg_gpt_trace_read": (None, [_P, C.POINTER(C.c_uint64), _SZ, _SZP]),
     "rg_linear_row_noalloc": (None, [_P, _P, _P, _P, _SZ, _SZ, _P]),
 }
 

@@ -2,6 +2,7 @@
 // KV-cache token step and the generate loop.  Mirrors GptConfig / GPTModel
 // (src/models/gpt.rs) and WasmGptTrainer::generate (src/wasm_api.rs:97-163).
 #include "rg_internal.cuh"
+#include "rg_gpt.h"
 #include "rg_gemm.cuh"
 #include "rg_decode_kernels.cuh"
 #include "rg_prefill_kernels.cuh"
@@ -11,55 +12,6 @@
 #include <string.h>
 
 #include <algorithm>
-
-struct rg_linear {
-    void* W = nullptr;  // [K][ldw] f32 or bf16
-    long long ldw = 0;
-    float* b = nullptr;  // [N]
-    int K = 0, N = 0;
-    int ksplit = 1, krows = 0;  // split of the token-step projection
-    float* parts = nullptr;     // [ksplit][Bmax][N]
-};
-
-struct rg_layer {
-    rg_linear qkv, o, fc1, fc2;
-    float *ln1g = nullptr, *ln1b = nullptr, *ln2g = nullptr, *ln2b = nullptr;
-};
-
-struct rg_gpt {
-    rg_ctx* ctx = nullptr;
-    rg_gpt_config cfg;
-    int V = 0, D = 0, L = 0, H = 0, hd = 0, C = 0, F = 0, Bmax = 1;
-    bool bf16 = false, loaded = false;
-    size_t wsize = 4;
-    long long ldt = 0;  // leading dimension of the two embedding tables
-    void *wte = nullptr, *wpe = nullptr;
-    float *lnfg = nullptr, *lnfb = nullptr;
-    rg_linear head;
-    std::vector<rg_layer> layers;
-    std::vector<void*> allocs;
-
-    // KV cache: [L][Bmax][H][C][hd], f32 or bf16
-    char *kc = nullptr, *vc = nullptr;
-    size_t kv_layer_bytes = 0;
-
-    // token-step state
-    float *xa = nullptr, *xb = nullptr, *ap = nullptr, *logits = nullptr;
-    uint32_t *tokens = nullptr, *picks = nullptr;
-    int *d_pos = nullptr, *d_pos_next = nullptr;
-    int NS = 1;
-    size_t pos = 0, curB = 0;
-    cudaGraphExec_t graph = nullptr;
-    size_t graphB = 0;
-    int kernels_per_step = 0;
-    bool use_graph = true;
-
-    // prompt-pass buffers, grown on demand
-    size_t rowsCap = 0;
-    float *px = nullptr, *pln = nullptr, *pqkv = nullptr, *pattn = nullptr, *ph = nullptr, *plast = nullptr;
-    float* plogits = nullptr;
-    size_t plogitsCap = 0;
-};
 
 static __global__ void rg_set_int2_kernel(int* a, int* b, int v) {
     *a = v;
@@ -212,6 +164,7 @@ extern "C" rg_status rg_gpt_destroy(rg_gpt* m) {
     cudaSetDevice(m->ctx->device);
     cudaStreamSynchronize(m->ctx->stream);
     if (m->graph) cudaGraphExecDestroy(m->graph);
+    rg_mega_destroy(m);
     for (void* p : m->allocs) cudaFree(p);
     delete m;
     return RG_OK;
@@ -318,7 +271,7 @@ extern "C" rg_status rg_gpt_load_params(rg_gpt* m, const float* const* data, con
     m->loaded = true;
     m->pos = 0;
     m->curB = 0;
-    return RG_OK;
+    return rg_mega_create(m);
 }
 
 // ---------------------------------------------------------------------------
@@ -614,6 +567,15 @@ static rg_status step_ready(rg_gpt* m, size_t steps) {
 static rg_status run_steps(rg_gpt* m, size_t steps) {
     const int B = (int)m->curB;
     cudaStream_t s = m->ctx->stream;
+    if (rg_mega_supports(m, B)) {
+        // one persistent cooperative kernel runs all the steps
+        rg_status st = rg_mega_run(m, B, m->pos, steps);
+        if (st == RG_OK) {
+            m->pos += steps;
+            return RG_OK;
+        }
+        if (st != RG_ERR_UNSUPPORTED) return st;
+    }
     if (!m->use_graph) {
         for (size_t i = 0; i < steps; i++) {
             m->ctx->launches += enqueue_step(m, B);
@@ -652,7 +614,7 @@ extern "C" rg_status rg_gpt_decode_step(rg_gpt* m, const uint32_t* tok, float* l
     if (logits) RG_CUDA(cudaMemcpyAsync(logits, m->logits, B * (size_t)m->V * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
     if (argmax) RG_CUDA(cudaMemcpyAsync(argmax, m->picks, B * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
     RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
-    return RG_OK;
+    return rg_mega_check(m);
 }
 
 extern "C" rg_status rg_gpt_decode_run(rg_gpt* m, size_t n_steps) {
@@ -686,7 +648,7 @@ extern "C" rg_status rg_gpt_read_tokens(rg_gpt* m, size_t from, size_t n, uint32
         RG_CUDA(cudaMemcpy2DAsync(out, n * 4, m->tokens + from, (size_t)m->C * 4, n * 4, m->curB, cudaMemcpyDeviceToHost,
                                   m->ctx->stream));
     RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
-    return RG_OK;
+    return rg_mega_check(m);
 }
 
 extern "C" size_t rg_gpt_position(const rg_gpt* m) { return m ? m->pos : 0; }
@@ -730,7 +692,7 @@ extern "C" rg_status rg_gpt_generate(rg_gpt* m, const uint32_t* prompt, size_t B
                                       m->ctx->stream));
         }
         RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
-        return RG_OK;
+        return rg_mega_check(m);
     }
     // The reference's loop proper (no mask, so no cache): every new id re-runs the
     // whole window of the last block_size ids (wasm_api.rs:102-118).
@@ -761,4 +723,16 @@ extern "C" double rg_gpt_decode_step_bytes(const rg_gpt* m, size_t B, double mea
     const double w = L * (12.0 * D * D + 13.0 * D) + D * V + V + 4.0 * D;
     const double kv = m->bf16 ? 2.0 : 4.0;
     return (double)m->wsize * w + (double)B * kv * 2.0 * L * D * mean_ctx;
+}
+
+extern "C" rg_status rg_gpt_trace_enable(rg_gpt* m, int on) {
+    if (!m) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    m->trace_on = on != 0;
+    return RG_OK;
+}
+
+extern "C" rg_status rg_gpt_trace_read(rg_gpt* m, uint64_t* out, size_t cap_rows, size_t* n_rows) {
+    if (!m || !out || !n_rows) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    rg_ctx_guard g(m->ctx);
+    return rg_mega_trace(m, (unsigned long long*)out, cap_rows, n_rows);
 }

@@ -1,0 +1,69 @@
+// Model state shared by the translation units of the GPT half of the library.
+#pragma once
+#include "rg_internal.cuh"
+
+struct rg_mega;  // persistent token-loop kernel state (rg_mega.cu)
+
+struct rg_linear {
+    void* W = nullptr;  // [K][ldw] f32 or bf16
+    long long ldw = 0;
+    float* b = nullptr;  // [N]
+    int K = 0, N = 0;
+    int ksplit = 1, krows = 0;  // split of the token-step projection
+    float* parts = nullptr;     // [ksplit][Bmax][N]
+};
+
+struct rg_layer {
+    rg_linear qkv, o, fc1, fc2;
+    float *ln1g = nullptr, *ln1b = nullptr, *ln2g = nullptr, *ln2b = nullptr;
+};
+
+struct rg_gpt {
+    rg_ctx* ctx = nullptr;
+    rg_gpt_config cfg;
+    int V = 0, D = 0, L = 0, H = 0, hd = 0, C = 0, F = 0, Bmax = 1;
+    bool bf16 = false, loaded = false;
+    size_t wsize = 4;
+    long long ldt = 0;  // leading dimension of the two embedding tables
+    void *wte = nullptr, *wpe = nullptr;
+    float *lnfg = nullptr, *lnfb = nullptr;
+    rg_linear head;
+    std::vector<rg_layer> layers;
+    std::vector<void*> allocs;
+
+    // KV cache: [L][Bmax][H][C][hd], f32 or bf16
+    char *kc = nullptr, *vc = nullptr;
+    size_t kv_layer_bytes = 0;
+
+    // token-step state
+    float *xa = nullptr, *xb = nullptr, *ap = nullptr, *logits = nullptr;
+    uint32_t *tokens = nullptr, *picks = nullptr;
+    int *d_pos = nullptr, *d_pos_next = nullptr;
+    int NS = 1;
+    size_t pos = 0, curB = 0;
+    cudaGraphExec_t graph = nullptr;
+    size_t graphB = 0;
+    int kernels_per_step = 0;
+    bool use_graph = true;
+
+    // prompt-pass buffers, grown on demand
+    size_t rowsCap = 0;
+    float *px = nullptr, *pln = nullptr, *pqkv = nullptr, *pattn = nullptr, *ph = nullptr, *plast = nullptr;
+    float* plogits = nullptr;
+    size_t plogitsCap = 0;
+
+    // persistent token-loop kernel (null when the model shape is outside its limits)
+    rg_mega* mega = nullptr;
+    bool use_mega = true;
+    bool trace_on = false;
+    uint32_t epoch = 0;  // token steps run so far by the persistent kernel (tags of its exchange buffers)
+};
+
+// rg_mega.cu
+rg_status rg_mega_create(rg_gpt* m);            // after the weights are on the device
+void rg_mega_destroy(rg_gpt* m);
+bool rg_mega_supports(const rg_gpt* m, int B);
+rg_status rg_mega_run(rg_gpt* m, int B, size_t pos0, size_t n_steps);  // enqueue n_steps token steps
+rg_status rg_mega_check(rg_gpt* m);
+rg_status rg_mega_trace(rg_gpt* m, unsigned long long* out, size_t cap_rows, size_t* n_rows);             // after a synchronise: did a bounded wait give up?
+

@@ -1,0 +1,1206 @@
+// Persistent token-loop kernel: one cooperative launch runs n token steps of the
+// KV-cache loop (src/wasm_api.rs:102-160 on a causal model) for up to 4
+// sequences, with no kernel boundary between layers or tokens.
+//
+// Design (sm_100a, one CTA per SM, 256 threads):
+//  * Every projection is split by OUTPUT COLUMNS only: a CTA owns a few 16-byte
+//    column groups of a matrix and all K rows of them, so it produces finished
+//    values (bias, activation and residual applied), never partial sums.
+//  * The weights are re-packed at load into one stream per CTA, in the order the
+//    CTA consumes them.  One elected thread moves that stream through a ring of
+//    32 KB shared-memory slots with bulk asynchronous copies (cp.async.bulk +
+//    mbarrier complete_tx).  The copies do not depend on activations, so they run
+//    ahead across stage and token boundaries: HBM keeps streaming while a stage
+//    waits for its input vector.
+//  * Stages exchange finished vectors through global memory as 64-bit words
+//    {value, tag}: the consumer polls the words it needs until their tag equals
+//    the tag of the current (token, layer).  Data and flag travel in one store,
+//    so there is no grid-wide barrier and no separate flag round trip.
+//  * Attention of one (sequence, head) runs in one CTA: cached K rows then V rows
+//    stream through the same ring (rows below the current position never change),
+//    exact two-pass softmax in shared memory, the new row's k/v come straight from
+//    the QKV stage and are appended to the cache.
+//  * The residual stream lives with the CTA that owns its columns.
+//  * Every wait (tagged words, mbarriers) is bounded: on expiry the CTA raises a
+//    global flag, drains its own copies and returns; the host reports RG_ERR_TIMEOUT.
+#include "rg_gpt.h"
+
+#include <string.h>
+
+#include <algorithm>
+
+#define MG_THREADS 256
+#define MG_SLOT_BYTES 32768
+#define MG_SPIN_LIMIT (1u << 21)
+#define MG_BMAX 4
+
+enum { MG_QKV = 0, MG_ATTN = 1, MG_OPROJ = 2, MG_FC1 = 3, MG_FC2 = 4, MG_HEAD = 5 };
+enum { MG_FIRST = 1, MG_LAST = 2, MG_LNPRE = 4 };  // LNPRE: the op's first chunk is [gamma | beta] of its LayerNorm
+
+typedef unsigned long long mg_word;  // (tag << 32) | payload bits
+
+struct mg_op {
+    int type, layer;
+    int nq, q0;  // projection: number of 16-byte column groups and the first one; attention: sequence b and head h
+    int K, kc, nchunks;
+    int flags;
+    long long src;  // byte offset of this group's packed weights
+    int aux;        // N=D stages: offset into the CTA's residual slice; head: rank of the CTA among head CTAs
+    int ln_off;     // MG_LNPRE: float offset of [gamma | beta] in the LayerNorm parameter block
+};
+
+// One entry of a CTA's copy schedule for a token step.
+struct mg_cdesc {
+    long long src;  // kind 0: byte offset into the packed weights; 1: byte offset into the LayerNorm block; 2: op index
+    int bytes;
+    int kind;
+};
+
+struct mg_params {
+    const mg_op* ops;
+    const int* cta_off;
+    const mg_cdesc* cds;  // per-CTA copy schedule of one token step
+    const int* cd_off;
+    const unsigned char* wpack;
+    const float* lnpack;  // [2L+1][2][D]: gamma | beta of ln1, ln2 per layer, then the final LayerNorm
+    unsigned long long* trace;  // optional [G][max_ops][4] timestamps of the last token step
+
+    const void *wte, *wpe;
+    long long ldt;
+    unsigned char *kc, *vc;
+    size_t kv_layer_bytes;
+    mg_word *buf_qkv, *buf_a, *buf_xc, *buf_h, *buf_xe, *buf_pick;
+    float* logits;
+    uint32_t *tokens, *picks;
+    int *d_pos, *d_pos_next;
+    int* abort_flag;
+    int V, D, L, H, hd, C, F;
+    int act;
+    int pos0, n_steps;
+    uint32_t epoch0;
+    int nslot, max_ops, max_cd, res_cap, n_pick_ctas;
+    int res_q0, res_nq;  // residual slice = column groups [res_q0, res_q0 + res_nq) of the N=D stages (per CTA: via ops)
+    float scale;
+};
+
+struct rg_mega {
+    int G = 0;
+    std::vector<mg_op> ops;
+    std::vector<int> cta_off;
+    std::vector<mg_cdesc> cds;
+    std::vector<int> cd_off;
+    mg_op* d_ops = nullptr;
+    int* d_cta_off = nullptr;
+    mg_cdesc* d_cds = nullptr;
+    int* d_cd_off = nullptr;
+    int max_cd = 0;
+    unsigned char* d_wpack = nullptr;
+    size_t wpack_bytes = 0;
+    float* d_lnpack = nullptr;
+    unsigned long long* d_trace = nullptr;
+    mg_word *buf_qkv = nullptr, *buf_a = nullptr, *buf_xc = nullptr, *buf_h = nullptr, *buf_xe = nullptr,
+            *buf_pick = nullptr;
+    size_t buf_bytes = 0;
+    mg_word* buf_base = nullptr;
+    int* d_abort = nullptr;
+    int max_ops = 0, res_cap = 0, n_pick_ctas = 0;
+    int nq_max[3] = {0, 0, 0};  // column groups per op for B = 1, 2, 4
+    int nslot = 0;
+    size_t smem_bytes = 0;
+    int built_for_B = 0;
+    std::vector<void*> allocs;
+};
+
+// ---------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t mg_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mg_mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mg_smem(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mg_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mg_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mg_mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(mg_smem(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mg_bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(mg_smem(dst)),
+                 "l"(src), "r"(bytes), "r"(mg_smem(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void mg_fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ mg_word mg_ld_word(const mg_word* p) {
+    mg_word v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void mg_st_word(mg_word* p, uint32_t tag, uint32_t payload) {
+    const mg_word v = ((mg_word)tag << 32) | payload;
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long mg_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ int mg_ld_flag(const int* p) {
+    int v;
+    asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+template <typename T>
+struct mg_vec;
+template <>
+struct mg_vec<float> {
+    static constexpr int N = 4;
+    __device__ __forceinline__ static void unpack(const uint4& v, float (&w)[4]) {
+        w[0] = __uint_as_float(v.x), w[1] = __uint_as_float(v.y), w[2] = __uint_as_float(v.z), w[3] = __uint_as_float(v.w);
+    }
+};
+template <>
+struct mg_vec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ __forceinline__ static void unpack(const uint4& v, float (&w)[8]) {
+        const unsigned int u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            w[2 * i] = __uint_as_float(u[i] << 16);
+            w[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------
+// CTA layout: warps 0-7 (256 threads) are consumers; warp 8 is the producer (one
+// elected lane issues the bulk copies).  Consumers synchronise among themselves
+// on named barrier 1, so the producer never has to take part.
+// ---------------------------------------------------------------------------
+#define MG_TOTAL_THREADS (MG_THREADS + 32)
+
+__device__ __forceinline__ void mg_csync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ bool mg_csync_or(bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)(pred ? 1 : 0))
+        : "memory");
+    return r != 0;
+}
+__device__ __forceinline__ void mg_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mg_smem(bar)) : "memory");
+}
+
+// Per-thread control state.  `dead` becomes CTA-wide at the next op boundary.
+struct mg_ctl {
+    int* abort_flag;
+    bool dead;
+};
+__device__ __forceinline__ void mg_give_up(mg_ctl& c) {
+    atomicExch(c.abort_flag, 1);
+    c.dead = true;
+}
+
+__device__ __forceinline__ int mg_attn_rows_per_chunk(int hd, int kvsize) { return MG_SLOT_BYTES / (hd * kvsize); }
+
+// Consumer view of the ring.
+struct mg_cons {
+    unsigned char* slots;
+    uint64_t *full, *empty;
+    int nslot, slot;
+    uint32_t parity;
+};
+__device__ __forceinline__ const unsigned char* mg_ring_wait(mg_cons& r, mg_ctl& ctl) {
+    uint32_t spins = 0;
+    while (!ctl.dead && !mg_mbar_try_wait(&r.full[r.slot], r.parity)) {
+        if (++spins > (MG_SPIN_LIMIT >> 3) || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) mg_give_up(ctl);
+    }
+    return r.slots + (size_t)r.slot * MG_SLOT_BYTES;
+}
+// Each consumer warp reports that it is done with the slot; the 8th report frees it.
+__device__ __forceinline__ void mg_ring_release(mg_cons& r) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mg_mbar_arrive(&r.empty[r.slot]);
+    if (++r.slot == r.nslot) r.slot = 0, r.parity ^= 1u;
+}
+
+// The producer: walks the CTA's copy schedule for every token of the run, waits for
+// a free slot, issues the copy.  K/V rows below the current position are final only
+// once the consumers have passed the same attention op of the previous token (they
+// append row pos-1 there); s_progress = token * nops + op index tells how far they are.
+__device__ void mg_producer(const mg_params& p, const mg_cdesc* cd, int ncd, const mg_op* ops, int nops,
+                            unsigned char* slots, uint64_t* full, uint64_t* empty, int nslot, volatile int* s_progress,
+                            volatile int* s_dead, int kvsize) {
+    int slot = 0;
+    uint32_t parity = 0, issued = 0;
+    bool stop = false;
+    const int rc = mg_attn_rows_per_chunk(p.hd, kvsize);
+    const size_t rb = (size_t)p.hd * kvsize;
+    for (int tok = 0; tok < p.n_steps && !stop; tok++) {
+        const int pos = p.pos0 + tok;
+        const int nk = (pos + rc - 1) / rc;
+        for (int i = 0; i < ncd && !stop; i++) {
+            const mg_cdesc d = cd[i];
+            int nch = 1;
+            const unsigned char *kbase = nullptr, *vbase = nullptr;
+            if (d.kind == 2) {
+                const mg_op& op = ops[(int)d.src];
+                if (tok > 0) {
+                    const int need = (tok - 1) * nops + (int)d.src;
+                    uint32_t spins = 0;
+                    while (*s_progress <= need) {
+                        if (++spins > MG_SPIN_LIMIT || *s_dead) {
+                            stop = true;
+                            break;
+                        }
+                    }
+                    if (stop) break;
+                    mg_fence_proxy_async();
+                }
+                nch = 2 * nk;
+                const size_t head_off = (((size_t)op.nq * p.H + op.q0) * p.C) * rb + (size_t)op.layer * p.kv_layer_bytes;
+                kbase = p.kc + head_off;
+                vbase = p.vc + head_off;
+            }
+            for (int j = 0; j < nch; j++) {
+                uint32_t spins = 0;
+                while (!mg_mbar_try_wait(&empty[slot], parity ^ 1u)) {
+                    if (++spins > (MG_SPIN_LIMIT >> 3) || *s_dead) {
+                        stop = true;
+                        break;
+                    }
+                }
+                if (stop) break;
+                const unsigned char* src;
+                uint32_t bytes;
+                if (d.kind == 0) src = p.wpack + d.src, bytes = (uint32_t)d.bytes;
+                else if (d.kind == 1) src = reinterpret_cast<const unsigned char*>(p.lnpack) + d.src, bytes = (uint32_t)d.bytes;
+                else {
+                    const int jj = j < nk ? j : j - nk;
+                    const int rows = min(rc, pos - jj * rc);
+                    src = (j < nk ? kbase : vbase) + (size_t)jj * rc * rb;
+                    bytes = (uint32_t)(rows * rb);
+                }
+                mg_mbar_expect_tx(&full[slot], bytes);
+                mg_bulk_g2s(slots + (size_t)slot * MG_SLOT_BYTES, src, bytes, &full[slot]);
+                issued++;
+                if (++slot == nslot) slot = 0, parity ^= 1u;
+            }
+        }
+    }
+    if (stop) {
+        // leaving early: wait (bounded) for the copies of ours that may still be in flight
+        const uint32_t n = issued < (uint32_t)nslot ? issued : (uint32_t)nslot;
+        for (uint32_t i = 0; i < n; i++) {
+            if (--slot < 0) slot = nslot - 1, parity ^= 1u;
+            uint32_t spins = 0;
+            while (!mg_mbar_try_wait(&full[slot], parity) && ++spins < (MG_SPIN_LIMIT >> 3)) {
+            }
+        }
+    }
+}
+
+// Poll n tagged words (src[i], i < n) until they carry `tag`; payloads to dst[i].
+__device__ __forceinline__ void mg_poll(const mg_word* src, int n, uint32_t tag, float* dst, mg_ctl& ctl) {
+    constexpr int U = 8;
+    for (int base = threadIdx.x; base < n; base += MG_THREADS * U) {
+        mg_word w[U];
+        uint32_t spins = 0;
+        bool ok;
+        do {
+            ok = true;
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int i = base + u * MG_THREADS;
+                if (i < n) {
+                    w[u] = mg_ld_word(src + i);
+                    ok = ok && (uint32_t)(w[u] >> 32) == tag;
+                }
+            }
+            if (!ok) {
+                if (++spins > MG_SPIN_LIMIT || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
+                    mg_give_up(ctl);
+                    break;
+                }
+            }
+        } while (!ok);
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int i = base + u * MG_THREADS;
+            if (i < n) dst[i] = __uint_as_float((uint32_t)w[u]);
+        }
+    }
+}
+
+// LayerNorm of xr[0..n) in shared memory, in place; gamma/beta in shared memory.
+// Statistics in ONE reduction round: with c = xr[0] as a common shift every thread
+// accumulates sum(x-c) and sum((x-c)^2) over its elements; mean = c + S1/n and the
+// biased variance = S2/n - (S1/n)^2 (eps inside the sqrt, src/ops/norm.rs:41-52).
+// The shift keeps the subtraction well conditioned: (c-mean)^2 <= n*var, so the
+// relative error of the variance stays below n*2^-24.  This is the one-pass idea of
+// fused::layer_norm_fused (src/backend/fused.rs:22-144) in the form that needs a
+// single cross-thread reduction instead of a chain of pairwise Welford merges.
+__device__ void mg_layernorm(float* xr, int n, const float* gamma, const float* beta, float* scratch /* 16 floats */) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const float c = xr[0];
+    float s1 = 0.f, s2 = 0.f;
+    for (int i = tid; i < n; i += MG_THREADS) {
+        const float d = xr[i] - c;
+        s1 += d;
+        s2 = fmaf(d, d, s2);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s1 += __shfl_xor_sync(RG_FULL_MASK, s1, o);
+        s2 += __shfl_xor_sync(RG_FULL_MASK, s2, o);
+    }
+    if (lane == 0) scratch[warp * 2] = s1, scratch[warp * 2 + 1] = s2;
+    mg_csync();
+    float t1 = 0.f, t2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < MG_THREADS / 32; i++) t1 += scratch[i * 2], t2 += scratch[i * 2 + 1];
+    const float rn = 1.f / (float)n;
+    const float m1 = t1 * rn;
+    const float mean = c + m1;
+    const float var = fmaxf(fmaf(-m1, m1, t2 * rn), 0.f);
+    const float inv = rsqrtf(var + 1e-5f);
+    for (int i = tid; i < n; i += MG_THREADS) xr[i] = (xr[i] - mean) * inv * gamma[i] + beta[i];
+    mg_csync();
+}
+
+__device__ __forceinline__ float mg_block_max(float v, float* scratch) {
+    v = rg_warp_max(v);
+    mg_csync();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    mg_csync();
+    float r = scratch[0];
+#pragma unroll
+    for (int i = 1; i < MG_THREADS / 32; i++) r = fmaxf(r, scratch[i]);
+    return r;
+}
+__device__ __forceinline__ float mg_block_sum(float v, float* scratch) {
+    v = rg_warp_sum(v);
+    mg_csync();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    mg_csync();
+    float r = 0.f;
+#pragma unroll
+    for (int i = 0; i < MG_THREADS / 32; i++) r += scratch[i];
+    return r;
+}
+
+// Sum N per-lane values across the warp with a halving exchange: while N is even each
+// step sends half of the values to the partner lane and keeps the other half, so N
+// halves per step; the remaining steps are plain butterflies.  On return v[0..N_out)
+// of lane l holds the warp sums of indices base(l) + [0, N_out).
+template <int N, int O>
+struct mg_halver {
+    __device__ __forceinline__ static void run(float (&v)[N], int lane, int& base, int& count) {
+        if constexpr (O == 0) {
+            count = N;
+        } else if constexpr (N % 2 == 0) {
+            constexpr int H = N / 2;
+            const bool upper = (lane & O) != 0;
+            float keep[H];
+#pragma unroll
+            for (int i = 0; i < H; i++) {
+                const float send = upper ? v[i] : v[i + H];
+                const float recv = __shfl_xor_sync(RG_FULL_MASK, send, O);
+                keep[i] = (upper ? v[i + H] : v[i]) + recv;
+            }
+            if (upper) base += H;
+            mg_halver<H, O / 2>::run(reinterpret_cast<float(&)[H]>(keep), lane, base, count);
+#pragma unroll
+            for (int i = 0; i < H; i++) v[i] = keep[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < N; i++) v[i] += __shfl_xor_sync(RG_FULL_MASK, v[i], O);
+            mg_halver<N, O / 2>::run(v, lane, base, count);
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
+template <typename WT, int B, int NQ>
+__global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(const mg_params p) {
+    constexpr int VEC = mg_vec<WT>::N;
+    constexpr int KVS = sizeof(WT);  // the KV cache has the weight dtype
+    constexpr int NOUT = B * NQ * VEC;  // finished values per group
+    static_assert(NOUT <= MG_THREADS, "one thread per finished value");
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cta = blockIdx.x;
+    const int XLEN = p.F;
+
+    // ---- shared memory carve-up (must match mg_smem_bytes on the host) ----
+    unsigned char* sp = smem_raw;
+    unsigned char* slots = sp;
+    sp += (size_t)p.nslot * MG_SLOT_BYTES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(sp);
+    uint64_t* empty = full + 8;
+    sp += 16 * 8;
+    mg_op* ops = reinterpret_cast<mg_op*>(sp);
+    sp += (size_t)p.max_ops * sizeof(mg_op);
+    mg_cdesc* cds = reinterpret_cast<mg_cdesc*>(sp);
+    sp += (size_t)p.max_cd * sizeof(mg_cdesc);
+    float* xs = reinterpret_cast<float*>(sp);  // [B][XLEN] input vector of the current stage
+    sp += (size_t)B * XLEN * 4;
+    float* xres = reinterpret_cast<float*>(sp);  // [B][res_cap] this CTA's slice of the residual stream
+    sp += (size_t)B * p.res_cap * 4;
+    float* sc = reinterpret_cast<float*>(sp);  // [C] attention scores / probabilities
+    sp += (size_t)p.C * 4;
+    float* go = reinterpret_cast<float*>(sp);  // [MG_THREADS * VEC] attention output partials
+    sp += (size_t)MG_THREADS * VEC * 4;
+    float* sqkv = reinterpret_cast<float*>(sp);  // q, k, v of the new row: 3 * hd
+    sp += 3 * 128 * 4;
+    float* red = reinterpret_cast<float*>(sp);  // [8][NOUT]
+    sp += 8 * NOUT * 4;
+    float* scratch = reinterpret_cast<float*>(sp);  // 32 floats
+    sp += 32 * 4;
+    float* bestv = reinterpret_cast<float*>(sp);  // [NOUT]
+    sp += NOUT * 4;
+    int* besti = reinterpret_cast<int*>(sp);  // [NOUT]
+    sp += NOUT * 4;
+    uint32_t* s_pick = reinterpret_cast<uint32_t*>(sp);  // [B]
+    sp += MG_BMAX * 4;
+    int* s_flags = reinterpret_cast<int*>(sp);  // [0] consumer progress, [1] dead
+    sp += 4 * 4;
+    float* pickbuf = reinterpret_cast<float*>(sp);  // [n_pick_ctas * B * 2]
+
+    const int op0 = p.cta_off[cta];
+    const int nops = p.cta_off[cta + 1] - op0;
+    const int cd0 = p.cd_off[cta];
+    const int ncd = p.cd_off[cta + 1] - cd0;
+    if (nops == 0) return;  // nothing depends on a CTA without work, and it depends on nothing
+    for (int i = tid; i < nops * (int)(sizeof(mg_op) / 4); i += MG_TOTAL_THREADS)
+        reinterpret_cast<int*>(ops)[i] = reinterpret_cast<const int*>(p.ops + op0)[i];
+    for (int i = tid; i < ncd * (int)(sizeof(mg_cdesc) / 4); i += MG_TOTAL_THREADS)
+        reinterpret_cast<int*>(cds)[i] = reinterpret_cast<const int*>(p.cds + cd0)[i];
+    if (tid == 0) {
+        for (int i = 0; i < p.nslot; i++) mg_mbar_init(&full[i], 1), mg_mbar_init(&empty[i], MG_THREADS / 32);
+        s_flags[0] = -1, s_flags[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == MG_THREADS / 32) {
+        // =================== producer warp ===================
+        if (lane == 0)
+            mg_producer(p, cds, ncd, ops, nops, slots, full, empty, p.nslot, s_flags, s_flags + 1, KVS);
+        __syncwarp();
+        __syncthreads();
+        return;
+    }
+
+    // =================== consumer warps ===================
+    mg_ctl ctl;
+    ctl.abort_flag = p.abort_flag;
+    ctl.dead = false;
+    mg_cons ring;
+    ring.slots = slots, ring.full = full, ring.empty = empty, ring.nslot = p.nslot, ring.slot = 0, ring.parity = 0;
+
+    const WT* wte = static_cast<const WT*>(p.wte);
+    const WT* wpe = static_cast<const WT*>(p.wpe);
+    // residual slice of this CTA: column groups of the N = D stages (same in every layer)
+    int res_q0 = 0, res_n = 0;
+    for (int i = 0; i < nops; i++)
+        if (ops[i].type == MG_OPROJ && ops[i].layer == 0) {
+            if (res_n == 0) res_q0 = ops[i].q0;
+            res_n += ops[i].nq * VEC;
+        }
+
+    for (int t = 0; t < p.n_steps && !ctl.dead; t++) {
+        const int pos = p.pos0 + t;
+        const uint32_t tagbase = (p.epoch0 + (uint32_t)t) * (uint32_t)(p.L + 1);
+
+        // ---- token + position embedding (src/models/gpt.rs:62-75), every CTA for itself ----
+        for (int b = 0; b < B; b++) {
+            const uint32_t tok = t == 0 ? p.tokens[(size_t)b * p.C + pos] : s_pick[b];
+            for (int k = tid; k < p.D; k += MG_THREADS)
+                xs[b * XLEN + k] = rg_to_float(wte[(size_t)tok * p.ldt + k]) + rg_to_float(wpe[(size_t)pos * p.ldt + k]);
+        }
+        mg_csync();
+        for (int i = tid; i < B * res_n; i += MG_THREADS) {
+            const int b = i / res_n, j = i - b * res_n;
+            xres[b * p.res_cap + j] = xs[b * XLEN + res_q0 * VEC + j];
+        }
+        // thread-local best logit of the head stage (thread tid < NOUT serves sequence tid / (NQ*VEC))
+        float my_best = -INFINITY;
+        int my_besti = 0x7fffffff;
+
+        for (int oi = 0; oi < nops; oi++) {
+            if (mg_csync_or(ctl.dead)) {
+                ctl.dead = true;
+                break;
+            }
+            if (tid == 0) *reinterpret_cast<volatile int*>(s_flags) = t * nops + oi;  // the producer reads this
+            const mg_op op = ops[oi];
+            const uint32_t tag = tagbase + (uint32_t)op.layer + 1u;
+            const bool tracing = p.trace != nullptr && t == p.n_steps - 1 && tid == 0;
+            unsigned long long* tr = tracing ? p.trace + ((size_t)cta * p.max_ops + oi) * 8 : nullptr;
+            long long wait_cyc = 0, poll_cyc = 0;
+            if (tracing) tr[0] = mg_globaltimer();
+            auto timed_wait = [&]() -> const unsigned char* {
+                const long long c0 = clock64();
+                const unsigned char* sl = mg_ring_wait(ring, ctl);
+                wait_cyc += clock64() - c0;
+                return sl;
+            };
+
+            if (op.type == MG_ATTN) {
+                // =================== attention of (sequence b, head h) ===================
+                const int b = op.nq, h = op.q0, HD = p.hd;
+                const int LPR = HD / VEC;            // lanes per cached row
+                const int RPP = MG_THREADS / LPR;    // rows per pass of the CTA
+                const int sub = tid % LPR, grp = tid / LPR;
+                // q, k, v of the new row from the QKV stage
+                for (int i = tid; i < 3 * HD; i += MG_THREADS) {
+                    const int which = i / HD, d = i - which * HD;
+                    const mg_word* src = p.buf_qkv + (size_t)b * 3 * p.D + which * p.D + h * HD + d;
+                    uint32_t spins = 0;
+                    mg_word w = mg_ld_word(src);
+                    while ((uint32_t)(w >> 32) != tag) {
+                        if (++spins > MG_SPIN_LIMIT || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
+                            mg_give_up(ctl);
+                            break;
+                        }
+                        w = mg_ld_word(src);
+                    }
+                    float v = __uint_as_float((uint32_t)w);
+                    if (which > 0 && KVS == 2) v = __bfloat162float(__float2bfloat16_rn(v));  // what the cache will hold
+                    sqkv[which * 128 + d] = v;
+                }
+                mg_csync();
+                const int rc = mg_attn_rows_per_chunk(HD, KVS);
+                const int nk = (pos + rc - 1) / rc;
+                if (tracing) tr[1] = mg_globaltimer();
+                float qf[VEC];
+#pragma unroll
+                for (int j = 0; j < VEC; j++) qf[j] = sqkv[sub * VEC + j];
+                // ---- scores: S = (q . k) * scale (src/nn/attention.rs:78-87); 4 rows per thread in flight ----
+                float mx = -INFINITY;
+                for (int j = 0; j < nk; j++) {
+                    const unsigned char* slot = timed_wait();
+                    const int rows = min(rc, pos - j * rc);
+                    for (int r0 = 0; r0 < rows; r0 += 4 * RPP) {
+                        float dot[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int rr = r0 + u * RPP + grp;
+                            dot[u] = 0.f;
+                            if (rr < rows) {
+                                float kf[VEC];
+                                mg_vec<WT>::unpack(*reinterpret_cast<const uint4*>(slot + ((size_t)rr * LPR + sub) * 16), kf);
+#pragma unroll
+                                for (int jj = 0; jj < VEC; jj++) dot[u] = fmaf(qf[jj], kf[jj], dot[u]);
+                            }
+                        }
+                        for (int o = LPR >> 1; o > 0; o >>= 1) {
+#pragma unroll
+                            for (int u = 0; u < 4; u++) dot[u] += __shfl_xor_sync(RG_FULL_MASK, dot[u], o);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int rr = r0 + u * RPP + grp;
+                            if (rr < rows) {
+                                const float sv = dot[u] * p.scale;
+                                mx = fmaxf(mx, sv);
+                                if (sub == 0) sc[j * rc + rr] = sv;
+                            }
+                        }
+                    }
+                    mg_ring_release(ring);
+                }
+                {   // the new row's score, by every warp for itself (cheap, saves a barrier)
+                    float dot = 0.f;
+                    for (int d = lane; d < HD; d += 32) dot = fmaf(sqkv[d], sqkv[128 + d], dot);
+                    dot = rg_warp_sum(dot) * p.scale;
+                    mx = fmaxf(mx, dot);
+                    if (tid == 0) sc[pos] = dot;
+                }
+                // ---- softmax over positions 0..pos (max-subtracted, src/ops/elementwise.rs:144-157) ----
+                mx = mg_block_max(mx, scratch);  // its barriers also publish sc[]
+                float sum = 0.f;
+                for (int i = tid; i <= pos; i += MG_THREADS) {
+                    const float e = __expf(sc[i] - mx);
+                    sc[i] = e;
+                    sum += e;
+                }
+                sum = mg_block_sum(sum, scratch);
+                if (tracing) tr[2] = mg_globaltimer();
+                // ---- output: P . v, two independent accumulators per thread ----
+                float acc[2][VEC];
+#pragma unroll
+                for (int j = 0; j < VEC; j++) acc[0][j] = 0.f, acc[1][j] = 0.f;
+                if (grp == 0) {
+                    const float pn = sc[pos];
+#pragma unroll
+                    for (int j = 0; j < VEC; j++) acc[0][j] = pn * sqkv[256 + sub * VEC + j];
+                }
+                for (int j = 0; j < nk; j++) {
+                    const unsigned char* slot = timed_wait();
+                    const int rows = min(rc, pos - j * rc);
+                    for (int r0 = grp; r0 < rows; r0 += 2 * RPP) {
+#pragma unroll
+                        for (int u = 0; u < 2; u++) {
+                            const int rr = r0 + u * RPP;
+                            if (rr < rows) {
+                                float vf[VEC];
+                                mg_vec<WT>::unpack(*reinterpret_cast<const uint4*>(slot + ((size_t)rr * LPR + sub) * 16), vf);
+                                const float pr = sc[j * rc + rr];
+#pragma unroll
+                                for (int jj = 0; jj < VEC; jj++) acc[u][jj] = fmaf(pr, vf[jj], acc[u][jj]);
+                            }
+                        }
+                    }
+                    mg_ring_release(ring);
+                }
+#pragma unroll
+                for (int j = 0; j < VEC; j++) go[grp * HD + sub * VEC + j] = acc[0][j] + acc[1][j];
+                mg_csync();
+                if (tid < HD) {
+                    float o0 = 0.f, o1 = 0.f;
+                    for (int g2 = 0; g2 < RPP; g2 += 2) o0 += go[g2 * HD + tid], o1 += go[(g2 + 1) * HD + tid];
+                    mg_st_word(p.buf_a + (size_t)b * p.D + h * HD + tid, tag, __float_as_uint(__fdividef(o0 + o1, sum)));
+                }
+                {   // append k, v at row pos, off the critical path (generic-proxy stores; later tokens read them
+                    // with bulk copies, which the producer issues only after this op is over)
+                    const size_t row = (((size_t)b * p.H + h) * p.C + pos) * HD;
+                    WT* kdst = reinterpret_cast<WT*>(p.kc + (size_t)op.layer * p.kv_layer_bytes) + row;
+                    WT* vdst = reinterpret_cast<WT*>(p.vc + (size_t)op.layer * p.kv_layer_bytes) + row;
+                    for (int i = tid; i < 2 * HD; i += MG_THREADS) {
+                        const int which = i / HD, d = i - which * HD;
+                        const float v = sqkv[(which + 1) * 128 + d];
+                        WT* dst = which == 0 ? kdst : vdst;
+                        if (KVS == 4) reinterpret_cast<float*>(dst)[d] = v;
+                        else reinterpret_cast<__nv_bfloat16*>(dst)[d] = __float2bfloat16_rn(v);
+                    }
+                    mg_fence_proxy_async();
+                }
+                if (tracing) tr[3] = mg_globaltimer(), tr[4] = (unsigned long long)wait_cyc, tr[5] = 0;
+                continue;
+            }
+
+            // =================== projection stages ===================
+            if (op.flags & MG_FIRST) {
+                // the stage's input vector, complete, into xs
+                const mg_word* src =
+                    op.type == MG_OPROJ ? p.buf_a : (op.type == MG_FC1 ? p.buf_xc : (op.type == MG_FC2 ? p.buf_h : p.buf_xe));
+                const int n_in = op.type == MG_FC2 ? p.F : p.D;
+                const uint32_t in_tag = (op.type == MG_QKV || op.type == MG_HEAD) ? tag - 1u : tag;  // previous block's output
+                const long long c0 = clock64();
+                if (!(op.type == MG_QKV && op.layer == 0))  // block 0 starts from the embedding already in xs
+                    for (int b = 0; b < B; b++) mg_poll(src + (size_t)b * n_in, n_in, in_tag, xs + b * XLEN, ctl);
+                mg_csync();
+                poll_cyc += clock64() - c0;
+                if (op.flags & MG_LNPRE) {
+                    const float* gb = reinterpret_cast<const float*>(timed_wait());
+                    for (int b = 0; b < B; b++) mg_layernorm(xs + b * XLEN, p.D, gb, gb + p.D, scratch);
+                    mg_ring_release(ring);
+                }
+            }
+            if (tracing) tr[1] = mg_globaltimer();
+            // ---- dot products of this group's columns over all K rows ----
+            float acc[NOUT];
+#pragma unroll
+            for (int i = 0; i < NOUT; i++) acc[i] = 0.f;
+            float bias_v = 0.f;
+            for (int j = 0; j < op.nchunks; j++) {
+                const unsigned char* slot = timed_wait();
+                const int kb = j * op.kc;
+                const int rows = min(op.kc, op.K - kb);
+                if (j == op.nchunks - 1 && tid < NOUT) {
+                    const int jq = tid % (NQ * VEC);
+                    if (jq < op.nq * VEC) bias_v = reinterpret_cast<const float*>(slot + (size_t)op.nq * rows * 16)[jq];
+                }
+#pragma unroll 2
+                for (int r = tid; r < rows; r += MG_THREADS) {
+                    float xv[B];
+#pragma unroll
+                    for (int b = 0; b < B; b++) xv[b] = xs[b * XLEN + kb + r];
+#pragma unroll
+                    for (int q = 0; q < NQ; q++) {
+                        if (q < op.nq) {
+                            float w[VEC];
+                            mg_vec<WT>::unpack(*reinterpret_cast<const uint4*>(slot + ((size_t)q * rows + r) * 16), w);
+#pragma unroll
+                            for (int b = 0; b < B; b++)
+#pragma unroll
+                                for (int jj = 0; jj < VEC; jj++)
+                                    acc[(b * NQ + q) * VEC + jj] = fmaf(xv[b], w[jj], acc[(b * NQ + q) * VEC + jj]);
+                        }
+                    }
+                }
+                mg_ring_release(ring);
+            }
+            // ---- sum over the 256 threads: halving exchange inside a warp, fixed order across warps ----
+            {
+                int base = 0, count = 0;
+                mg_halver<NOUT, 16>::run(acc, lane, base, count);
+                // lanes that differ only in the bits consumed by plain butterflies hold the same sums: the lowest writes
+                bool writer = true;
+                {
+                    int n = NOUT, o = 16;
+                    while (o > 0 && n % 2 == 0) n /= 2, o >>= 1;
+                    if (o > 0) writer = (lane & (2 * o - 1)) == 0;
+                }
+                if (writer)
+                    for (int i = 0; i < count; i++) red[warp * NOUT + base + i] = acc[i];
+            }
+            mg_csync();
+            if (tracing) tr[2] = mg_globaltimer();
+            if (tid < NOUT) {
+                const int b = tid / (NQ * VEC), jq = tid - b * (NQ * VEC);
+                if (jq < op.nq * VEC) {
+                    float s = bias_v;
+#pragma unroll
+                    for (int w2 = 0; w2 < MG_THREADS / 32; w2++) s += red[w2 * NOUT + tid];
+                    const int col = op.q0 * VEC + jq;
+                    if (op.type == MG_QKV) {
+                        mg_st_word(p.buf_qkv + (size_t)b * 3 * p.D + col, tag, __float_as_uint(s));
+                    } else if (op.type == MG_OPROJ) {
+                        const float v = xres[b * p.res_cap + op.aux + jq] + s;
+                        xres[b * p.res_cap + op.aux + jq] = v;
+                        mg_st_word(p.buf_xc + (size_t)b * p.D + col, tag, __float_as_uint(v));
+                    } else if (op.type == MG_FC1) {
+                        const float v = rg_apply_act(s, p.act);
+                        mg_st_word(p.buf_h + (size_t)b * p.F + col, tag, __float_as_uint(v));
+                    } else if (op.type == MG_FC2) {
+                        const float v = xres[b * p.res_cap + op.aux + jq] + s;
+                        xres[b * p.res_cap + op.aux + jq] = v;
+                        mg_st_word(p.buf_xe + (size_t)b * p.D + col, tag, __float_as_uint(v));
+                    } else if (col < p.V) {  // MG_HEAD
+                        p.logits[(size_t)b * p.V + col] = s;
+                        if (s > my_best || (s == my_best && col < my_besti)) my_best = s, my_besti = col;
+                    }
+                }
+            }
+            if (tracing) tr[3] = mg_globaltimer(), tr[4] = (unsigned long long)wait_cyc, tr[5] = (unsigned long long)poll_cyc;
+            if (op.type == MG_HEAD && (op.flags & MG_LAST)) {
+                // this CTA's best logit per sequence -> its slot of the pick buffer
+                if (tid < NOUT) bestv[tid] = my_best, besti[tid] = my_besti;
+                mg_csync();
+                if (tid < B) {
+                    float bv = -INFINITY;
+                    int bi = 0x7fffffff;
+                    for (int i = 0; i < NQ * VEC; i++) {
+                        const float v = bestv[tid * NQ * VEC + i];
+                        const int ix = besti[tid * NQ * VEC + i];
+                        if (v > bv || (v == bv && ix < bi)) bv = v, bi = ix;
+                    }
+                    mg_word* dst = p.buf_pick + ((size_t)op.aux * B + tid) * 2;
+                    mg_st_word(dst, tagbase + (uint32_t)p.L + 1u, __float_as_uint(bv));
+                    mg_st_word(dst + 1, tagbase + (uint32_t)p.L + 1u, (uint32_t)bi);
+                }
+            }
+        }
+        if (ctl.dead) break;
+
+        // ---- greedy pick (top_k = 1 of src/wasm_api.rs:120-156): best over all CTAs, lowest index on ties ----
+        mg_poll(p.buf_pick, p.n_pick_ctas * B * 2, tagbase + (uint32_t)p.L + 1u, pickbuf, ctl);
+        mg_csync();
+        if (warp < B) {  // warp b scans the candidates of sequence b
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int r = lane; r < p.n_pick_ctas; r += 32) {
+                const float v = pickbuf[(r * B + warp) * 2];
+                const int ix = (int)__float_as_uint(pickbuf[(r * B + warp) * 2 + 1]);
+                if (v > bv || (v == bv && ix < bi)) bv = v, bi = ix;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(RG_FULL_MASK, bv, o);
+                const int oi2 = __shfl_xor_sync(RG_FULL_MASK, bi, o);
+                if (ov > bv || (ov == bv && oi2 < bi)) bv = ov, bi = oi2;
+            }
+            if (lane == 0) {
+                if (bi == 0x7fffffff) bi = 0;
+                s_pick[warp] = (uint32_t)bi;
+                if (cta == 0) {
+                    p.picks[warp] = (uint32_t)bi;
+                    if (pos + 1 < p.C) p.tokens[(size_t)warp * p.C + pos + 1] = (uint32_t)bi;
+                }
+            }
+        }
+        mg_csync();
+    }
+
+    // ---- exit ----
+    const bool died = mg_csync_or(ctl.dead);
+    if (tid == 0) {
+        if (died) *reinterpret_cast<volatile int*>(s_flags + 1) = 1;  // tells the producer to stop and drain
+        else if (cta == 0) {
+            *p.d_pos_next = p.pos0 + p.n_steps;
+            *p.d_pos = p.pos0 + p.n_steps - 1;
+        }
+    }
+    __syncthreads();  // joins the producer warp: no copy of ours is in flight past this point
+}
+
+// ---------------------------------------------------------------------------
+// packing: row-major [K][ldw] -> per-CTA streams of [chunk][column group][row][16 bytes]
+// ---------------------------------------------------------------------------
+template <typename WT>
+static __global__ void mg_pack_kernel(const WT* __restrict__ W, long long ldw, const float* __restrict__ bias, int N,
+                                      const mg_op* __restrict__ ops, const int* __restrict__ cta_off, int type, int layer,
+                                      unsigned char* __restrict__ dst) {
+    constexpr int VEC = 16 / sizeof(WT);
+    const int cta = blockIdx.x;
+    for (int oi = cta_off[cta]; oi < cta_off[cta + 1]; oi++) {
+        const mg_op op = ops[oi];
+        if (op.type != type || op.layer != layer) continue;
+        const int total = op.nq * op.K;
+        for (int e = threadIdx.x; e < total; e += blockDim.x) {
+            const int k = e / op.nq, q = e - k * op.nq;
+            const int j = k / op.kc, r = k - j * op.kc;
+            const int rows = min(op.kc, op.K - j * op.kc);
+            const uint4 v = *reinterpret_cast<const uint4*>(W + (size_t)k * ldw + (size_t)(op.q0 + q) * VEC);
+            *reinterpret_cast<uint4*>(dst + op.src + ((size_t)j * op.nq * op.kc + (size_t)q * rows + r) * 16) = v;
+        }
+        // trailer of the last chunk: the f32 bias of the group's columns
+        float* tail = reinterpret_cast<float*>(dst + op.src + (size_t)op.nq * op.K * 16);
+        for (int e = threadIdx.x; e < op.nq * VEC; e += blockDim.x) {
+            const int col = op.q0 * VEC + e;
+            tail[e] = col < N ? bias[col] : 0.f;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host: program builder
+// ---------------------------------------------------------------------------
+static int mg_variant(int B) { return B == 1 ? 0 : (B == 2 ? 1 : (B == 4 ? 2 : -1)); }
+static int mg_nq_for(bool bf16, int B) {
+    if (!bf16) return B == 1 ? 6 : (B == 2 ? 4 : 2);
+    return B == 1 ? 3 : (B == 2 ? 2 : 1);
+}
+
+static rg_status mg_dalloc(rg_mega* g, void** p, size_t bytes) {
+    cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+    if (e != cudaSuccess) {
+        *p = nullptr;
+        return rg_fail(RG_ERR_BACKEND, "Failed to allocate %zu bytes of CUDA memory: %s", bytes, cudaGetErrorString(e));
+    }
+    g->allocs.push_back(*p);
+    return RG_OK;
+}
+
+static size_t mg_smem_bytes(const rg_gpt* m, int B, int NQ, int nslot, int max_ops, int max_cd, int res_cap, int n_pick) {
+    const int VEC = m->bf16 ? 8 : 4;
+    const int NOUT = B * NQ * VEC;
+    size_t s = (size_t)nslot * MG_SLOT_BYTES + 128 + (size_t)max_ops * sizeof(mg_op) + (size_t)max_cd * sizeof(mg_cdesc);
+    s += (size_t)B * m->F * 4 + (size_t)B * res_cap * 4 + (size_t)m->C * 4 + (size_t)MG_THREADS * VEC * 4 + 3 * 128 * 4;
+    s += 8 * (size_t)NOUT * 4 + 32 * 4 + 2 * (size_t)NOUT * 4 + MG_BMAX * 4 + 16 + (size_t)n_pick * B * 2 * 4;
+    return s + 128;
+}
+
+// Build the per-CTA op lists for batch B (the column-group limit per op depends on B).
+static void mg_build_program(rg_gpt* m, rg_mega* g, int B) {
+    const int G = g->G, VEC = m->bf16 ? 8 : 4, NQ = mg_nq_for(m->bf16, B);
+    std::vector<std::vector<mg_op>> per(G);
+    int rot = 0;
+    auto add_projection = [&](int type, int layer, int K, int N, int fixed_rot, int ln_off) {
+        const int Q = rg_cdiv(N, VEC);
+        const int base = Q / G, extra = Q % G;
+        const int r0 = fixed_rot >= 0 ? fixed_rot : rot;
+        const int active = std::min(G, Q);
+        for (int r = 0; r < active; r++) {
+            const int c = (r + r0) % G;
+            int nq = base + (r < extra ? 1 : 0);
+            int q = r * base + std::min(r, extra);
+            int aux = 0;
+            bool first = true;
+            while (nq > 0) {
+                mg_op op;
+                memset(&op, 0, sizeof(op));
+                op.type = type, op.layer = layer, op.K = K;
+                op.nq = std::min(nq, NQ), op.q0 = q;
+                const size_t budget = MG_SLOT_BYTES - 256;  // room for the bias trailer of the last chunk
+                const size_t bytes = (size_t)op.nq * K * 16;
+                const int nch = (int)((bytes + budget - 1) / budget);
+                int kc = rg_cdiv(K, nch);
+                kc = (kc + 31) / 32 * 32;
+                while ((size_t)op.nq * kc * 16 > budget) kc -= 32;
+                op.kc = std::max(kc, 1);
+                op.nchunks = rg_cdiv(K, op.kc);
+                op.flags = first ? MG_FIRST : 0;
+                if (first && ln_off >= 0) op.flags |= MG_LNPRE, op.ln_off = ln_off;
+                op.aux = type == MG_HEAD ? r : aux;
+                first = false;
+                aux += op.nq * VEC;
+                q += op.nq, nq -= op.nq;
+                if (nq == 0) op.flags |= MG_LAST;
+                per[c].push_back(op);
+            }
+        }
+        if (fixed_rot < 0) rot = (rot + extra) % G;
+        return active;
+    };
+    const int extraD = rg_cdiv(m->D, VEC) % G;
+    rot = extraD;  // stages with N != D put their larger shares on other CTAs than the N = D stages do
+    for (int l = 0; l < m->L; l++) {
+        add_projection(MG_QKV, l, m->D, 3 * m->D, -1, (4 * l) * m->D);
+        for (int pr = 0; pr < B * m->H; pr++) {  // one CTA per (sequence, head), from the top of the grid down
+            mg_op op;
+            memset(&op, 0, sizeof(op));
+            op.type = MG_ATTN, op.layer = l, op.nq = pr / m->H, op.q0 = pr % m->H;
+            op.flags = MG_FIRST | MG_LAST;
+            per[(G - 1) - (pr % G)].push_back(op);
+        }
+        add_projection(MG_OPROJ, l, m->D, m->D, 0, -1);
+        add_projection(MG_FC1, l, m->D, m->F, -1, (4 * l + 2) * m->D);
+        add_projection(MG_FC2, l, m->F, m->D, 0, -1);
+    }
+    g->n_pick_ctas = add_projection(MG_HEAD, m->L, m->D, m->V, -1, (4 * m->L) * m->D);
+    g->ops.clear();
+    g->cta_off.assign(G + 1, 0);
+    g->max_ops = 1;
+    g->res_cap = VEC;
+    size_t off = 0;
+    for (int c = 0; c < G; c++) {
+        g->cta_off[c] = (int)g->ops.size();
+        int res = 0;
+        for (mg_op& op : per[c]) {
+            if (op.type != MG_ATTN) {
+                op.src = (long long)off;
+                off += (size_t)op.nq * op.K * 16 + (size_t)op.nq * VEC * 4;
+            }
+            if (op.type == MG_OPROJ && op.layer == 0) res += op.nq * VEC;
+            g->ops.push_back(op);
+        }
+        g->max_ops = std::max(g->max_ops, (int)per[c].size());
+        g->res_cap = std::max(g->res_cap, res);
+    }
+    g->cta_off[G] = (int)g->ops.size();
+    g->wpack_bytes = off;
+    // the copy schedule: one entry per chunk of a projection, one per attention op (expanded on the device)
+    g->cds.clear();
+    g->cd_off.assign(G + 1, 0);
+    g->max_cd = 1;
+    for (int c = 0; c < G; c++) {
+        g->cd_off[c] = (int)g->cds.size();
+        for (int oi = g->cta_off[c]; oi < g->cta_off[c + 1]; oi++) {
+            const mg_op& op = g->ops[oi];
+            if (op.type == MG_ATTN) {
+                g->cds.push_back({(long long)(oi - g->cta_off[c]), 0, 2});
+                continue;
+            }
+            if (op.flags & MG_LNPRE) g->cds.push_back({(long long)op.ln_off * 4, 2 * m->D * 4, 1});
+            for (int j = 0; j < op.nchunks; j++) {
+                const int rows = std::min(op.kc, op.K - j * op.kc);
+                int bytes = op.nq * rows * 16;
+                if (j == op.nchunks - 1) bytes += op.nq * VEC * 4;
+                g->cds.push_back({op.src + (long long)j * op.nq * op.kc * 16, bytes, 0});
+            }
+        }
+        g->max_cd = std::max(g->max_cd, (int)g->cds.size() - g->cd_off[c]);
+    }
+    g->cd_off[G] = (int)g->cds.size();
+}
+
+template <typename WT>
+static void mg_pack_all(rg_gpt* m, rg_mega* g) {
+    cudaStream_t s = m->ctx->stream;
+    for (int l = 0; l < m->L; l++) {
+        rg_layer& y = m->layers[l];
+        const rg_linear* lins[4] = {&y.qkv, &y.o, &y.fc1, &y.fc2};
+        const int types[4] = {MG_QKV, MG_OPROJ, MG_FC1, MG_FC2};
+        for (int i = 0; i < 4; i++)
+            mg_pack_kernel<WT><<<g->G, 256, 0, s>>>((const WT*)lins[i]->W, lins[i]->ldw, lins[i]->b, lins[i]->N, g->d_ops,
+                                                    g->d_cta_off, types[i], l, g->d_wpack);
+        float* ln = g->d_lnpack + (size_t)4 * l * m->D;
+        cudaMemcpyAsync(ln, y.ln1g, m->D * 4, cudaMemcpyDeviceToDevice, s);
+        cudaMemcpyAsync(ln + m->D, y.ln1b, m->D * 4, cudaMemcpyDeviceToDevice, s);
+        cudaMemcpyAsync(ln + 2 * m->D, y.ln2g, m->D * 4, cudaMemcpyDeviceToDevice, s);
+        cudaMemcpyAsync(ln + 3 * m->D, y.ln2b, m->D * 4, cudaMemcpyDeviceToDevice, s);
+    }
+    mg_pack_kernel<WT><<<g->G, 256, 0, s>>>((const WT*)m->head.W, m->head.ldw, m->head.b, m->head.N, g->d_ops, g->d_cta_off,
+                                            MG_HEAD, m->L, g->d_wpack);
+    float* lnf = g->d_lnpack + (size_t)4 * m->L * m->D;
+    cudaMemcpyAsync(lnf, m->lnfg, m->D * 4, cudaMemcpyDeviceToDevice, s);
+    cudaMemcpyAsync(lnf + m->D, m->lnfb, m->D * 4, cudaMemcpyDeviceToDevice, s);
+    m->ctx->launches += 4 * m->L + 1;
+}
+
+template <typename WT, int B, int NQ>
+static cudaError_t mg_launch(rg_gpt* m, rg_mega* g, mg_params& prm) {
+    auto kern = rg_token_loop_kernel<WT, B, NQ>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g->smem_bytes);
+    if (e != cudaSuccess) return e;
+    void* args[] = {&prm};
+    return cudaLaunchCooperativeKernel((void*)kern, dim3(g->G), dim3(MG_TOTAL_THREADS), args, g->smem_bytes, m->ctx->stream);
+}
+
+// (Re)build program, packed weights and exchange buffers for batch B.
+static rg_status mg_prepare(rg_gpt* m, int B) {
+    rg_mega* g = m->mega;
+    if (g->built_for_B == B) return RG_OK;
+    RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    for (void* p : g->allocs) cudaFree(p);
+    g->allocs.clear();
+    g->built_for_B = 0;
+    mg_build_program(m, g, B);
+    const int NQ = mg_nq_for(m->bf16, B);
+    // ring depth: as many 32 KB slots as fit beside the rest (at most 6)
+    g->nslot = 0;
+    for (int ns = 6; ns >= 2; ns--) {
+        const size_t need = mg_smem_bytes(m, B, NQ, ns, g->max_ops, g->max_cd, g->res_cap, g->n_pick_ctas);
+        if (need <= 227 * 1024) {
+            g->nslot = ns;
+            g->smem_bytes = need;
+            break;
+        }
+    }
+    if (g->nslot == 0) return rg_fail(RG_ERR_UNSUPPORTED, "model too large for the persistent token-loop kernel's shared memory");
+    RG_TRY(mg_dalloc(g, (void**)&g->d_ops, g->ops.size() * sizeof(mg_op)));
+    RG_TRY(mg_dalloc(g, (void**)&g->d_cta_off, (g->G + 1) * sizeof(int)));
+    RG_TRY(mg_dalloc(g, (void**)&g->d_cds, g->cds.size() * sizeof(mg_cdesc)));
+    RG_TRY(mg_dalloc(g, (void**)&g->d_cd_off, (g->G + 1) * sizeof(int)));
+    RG_TRY(mg_dalloc(g, (void**)&g->d_wpack, g->wpack_bytes));
+    RG_TRY(mg_dalloc(g, (void**)&g->d_lnpack, (size_t)(4 * m->L + 2) * m->D * 4));
+    RG_TRY(mg_dalloc(g, (void**)&g->d_trace, (size_t)g->G * g->max_ops * 8 * 8));
+    RG_CUDA(cudaMemset(g->d_trace, 0, (size_t)g->G * g->max_ops * 8 * 8));
+    RG_TRY(mg_dalloc(g, (void**)&g->d_abort, 16));
+    const size_t words = (size_t)B * (3 * m->D + m->D + m->D + m->F + m->D) + (size_t)g->n_pick_ctas * B * 2;
+    RG_TRY(mg_dalloc(g, (void**)&g->buf_base, words * 8));
+    g->buf_bytes = words * 8;
+    mg_word* w = g->buf_base;
+    g->buf_qkv = w, w += (size_t)B * 3 * m->D;
+    g->buf_a = w, w += (size_t)B * m->D;
+    g->buf_xc = w, w += (size_t)B * m->D;
+    g->buf_h = w, w += (size_t)B * m->F;
+    g->buf_xe = w, w += (size_t)B * m->D;
+    g->buf_pick = w;
+    RG_CUDA(cudaMemset(g->buf_base, 0, g->buf_bytes));
+    RG_CUDA(cudaMemset(g->d_abort, 0, 16));
+    m->epoch = 0;
+    RG_CUDA(cudaMemcpy(g->d_ops, g->ops.data(), g->ops.size() * sizeof(mg_op), cudaMemcpyHostToDevice));
+    RG_CUDA(cudaMemcpy(g->d_cta_off, g->cta_off.data(), (g->G + 1) * sizeof(int), cudaMemcpyHostToDevice));
+    RG_CUDA(cudaMemcpy(g->d_cds, g->cds.data(), g->cds.size() * sizeof(mg_cdesc), cudaMemcpyHostToDevice));
+    RG_CUDA(cudaMemcpy(g->d_cd_off, g->cd_off.data(), (g->G + 1) * sizeof(int), cudaMemcpyHostToDevice));
+    if (m->bf16) mg_pack_all<__nv_bfloat16>(m, g);
+    else mg_pack_all<float>(m, g);
+    RG_CUDA(cudaGetLastError());
+    RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    g->built_for_B = B;
+    return RG_OK;
+}
+
+bool rg_mega_supports(const rg_gpt* m, int B) {
+    return m->mega != nullptr && m->use_mega && m->cfg.causal && mg_variant(B) >= 0 && m->hd <= 128;
+}
+
+rg_status rg_mega_create(rg_gpt* m) {
+    rg_mega_destroy(m);
+    const char* mode = getenv("RG_B200_DECODE");
+    m->use_mega = !(mode && strcmp(mode, "graph") == 0);
+    if (!m->cfg.causal) return RG_OK;
+    m->mega = new rg_mega();
+    m->mega->G = m->ctx->sm_count;
+    return RG_OK;
+}
+
+void rg_mega_destroy(rg_gpt* m) {
+    if (!m->mega) return;
+    for (void* p : m->mega->allocs) cudaFree(p);
+    delete m->mega;
+    m->mega = nullptr;
+}
+
+rg_status rg_mega_run(rg_gpt* m, int B, size_t pos0, size_t n_steps) {
+    if (n_steps == 0) return RG_OK;
+    rg_status st = mg_prepare(m, B);
+    if (st == RG_ERR_UNSUPPORTED) {  // fall back to the graph path for this model from now on
+        m->use_mega = false;
+        return st;
+    }
+    RG_TRY(st);
+    rg_mega* g = m->mega;
+    // tags are (epoch * (L+1) + layer + 1) in 32 bits: start over long before they wrap
+    if (((uint64_t)m->epoch + n_steps + 1) * (uint64_t)(m->L + 1) >= 0xfffffff0ull) {
+        RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+        RG_CUDA(cudaMemset(g->buf_base, 0, g->buf_bytes));
+        m->epoch = 0;
+    }
+    mg_params prm;
+    memset(&prm, 0, sizeof(prm));
+    prm.ops = g->d_ops, prm.cta_off = g->d_cta_off, prm.wpack = g->d_wpack, prm.lnpack = g->d_lnpack;
+    prm.cds = g->d_cds, prm.cd_off = g->d_cd_off, prm.max_cd = g->max_cd;
+    prm.trace = m->trace_on ? g->d_trace : nullptr;
+    prm.wte = m->wte, prm.wpe = m->wpe, prm.ldt = m->ldt;
+    prm.kc = (unsigned char*)m->kc, prm.vc = (unsigned char*)m->vc, prm.kv_layer_bytes = m->kv_layer_bytes;
+    prm.buf_qkv = g->buf_qkv, prm.buf_a = g->buf_a, prm.buf_xc = g->buf_xc, prm.buf_h = g->buf_h, prm.buf_xe = g->buf_xe;
+    prm.buf_pick = g->buf_pick;
+    prm.logits = m->logits, prm.tokens = m->tokens, prm.picks = m->picks, prm.d_pos = m->d_pos, prm.d_pos_next = m->d_pos_next;
+    prm.abort_flag = g->d_abort;
+    prm.V = m->V, prm.D = m->D, prm.L = m->L, prm.H = m->H, prm.hd = m->hd, prm.C = m->C, prm.F = m->F;
+    prm.act = m->cfg.activation;
+    prm.pos0 = (int)pos0, prm.n_steps = (int)n_steps, prm.epoch0 = m->epoch;
+    prm.nslot = g->nslot, prm.max_ops = g->max_ops, prm.res_cap = g->res_cap, prm.n_pick_ctas = g->n_pick_ctas;
+    prm.scale = 1.f / sqrtf((float)m->hd);
+    cudaError_t e;
+    if (!m->bf16) {
+        if (B == 1) e = mg_launch<float, 1, 6>(m, g, prm);
+        else if (B == 2) e = mg_launch<float, 2, 4>(m, g, prm);
+        else e = mg_launch<float, 4, 2>(m, g, prm);
+    } else {
+        if (B == 1) e = mg_launch<__nv_bfloat16, 1, 3>(m, g, prm);
+        else if (B == 2) e = mg_launch<__nv_bfloat16, 2, 2>(m, g, prm);
+        else e = mg_launch<__nv_bfloat16, 4, 1>(m, g, prm);
+    }
+    if (e != cudaSuccess)
+        return rg_fail(RG_ERR_BACKEND, "persistent token-loop kernel launch failed: %s", cudaGetErrorString(e));
+    m->epoch += (uint32_t)n_steps;
+    m->ctx->launches += 1;
+    return RG_OK;
+}
+
+rg_status rg_mega_check(rg_gpt* m) {
+    if (!m->mega || !m->mega->d_abort || !m->mega->built_for_B) return RG_OK;
+    int flag = 0;
+    RG_CUDA(cudaMemcpyAsync(&flag, m->mega->d_abort, sizeof(int), cudaMemcpyDeviceToHost, m->ctx->stream));
+    RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    if (flag) {
+        cudaMemsetAsync(m->mega->d_abort, 0, sizeof(int), m->ctx->stream);
+        cudaMemsetAsync(m->mega->buf_base, 0, m->mega->buf_bytes, m->ctx->stream);
+        m->epoch = 0;
+        return rg_fail(RG_ERR_TIMEOUT, "a bounded wait inside the persistent token-loop kernel gave up; the step was abandoned");
+    }
+    return RG_OK;
+}
+
+// Timestamps (ns, %globaltimer) of the last token step of the last run, per CTA and op:
+// [start, input ready, dot products done, outputs stored] then SM cycles spent waiting for ring slots and
+// for the input vector.  Rows of 10: cta, op index, type, layer, t0..t3, wait cycles, poll cycles.
+rg_status rg_mega_trace(rg_gpt* m, unsigned long long* out, size_t cap_rows, size_t* n_rows) {
+    rg_mega* g = m->mega;
+    *n_rows = 0;
+    if (!g || !g->built_for_B || !g->d_trace) return RG_OK;
+    std::vector<unsigned long long> raw((size_t)g->G * g->max_ops * 8);
+    RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    RG_CUDA(cudaMemcpy(raw.data(), g->d_trace, raw.size() * 8, cudaMemcpyDeviceToHost));
+    size_t n = 0;
+    for (int c = 0; c < g->G; c++)
+        for (int oi = g->cta_off[c]; oi < g->cta_off[c + 1]; oi++) {
+            if (n >= cap_rows) break;
+            const mg_op& op = g->ops[oi];
+            const unsigned long long* t = &raw[((size_t)c * g->max_ops + (oi - g->cta_off[c])) * 8];
+            unsigned long long* o = out + n * 10;
+            o[0] = c, o[1] = oi - g->cta_off[c], o[2] = op.type, o[3] = op.layer;
+            o[4] = t[0], o[5] = t[1], o[6] = t[2], o[7] = t[3], o[8] = t[4], o[9] = t[5];
+            n++;
+        }
+    *n_rows = n;
+    return RG_OK;
+}

@@ -139,5 +139,16 @@ class GPTModel:
                                         float(temperature), int(top_k), int(seed), out.ctypes.data_as(_lib._U32P)))
         return out[0] if single else out
 
+    def trace(self, on: bool = True) -> None:
+        """Record per-stage device timestamps of the last token step of each decode_run."""
+        check(self._lib.rg_gpt_trace_enable(self._h, 1 if on else 0))
+
+    def read_trace(self, cap_rows: int = 1 << 16) -> np.ndarray:
+        """Rows [cta, op, stage, layer, t_start, t_input, t_dots, t_stored (ns), chunk-wait cycles, poll cycles]."""
+        out = np.zeros((cap_rows, 10), dtype=np.uint64)
+        n = C.c_size_t(0)
+        check(self._lib.rg_gpt_trace_read(self._h, out.ctypes.data_as(C.POINTER(C.c_uint64)), cap_rows, C.byref(n)))
+        return out[: n.value]
+
     def decode_step_bytes(self, batch: int, mean_ctx: float) -> float:
         return float(self._lib.rg_gpt_decode_step_bytes(self._h, int(batch), float(mean_ctx)))
