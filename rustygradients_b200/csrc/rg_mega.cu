@@ -46,7 +46,7 @@ struct mg_op {
     int flags;
     long long src;  // byte offset of this group's packed weights
     int aux;        // N=D stages: offset into the CTA's residual slice; head: rank of the CTA among head CTAs
-    int ln_off;     // MG_LNPRE: float offset of [gamma | beta] in the LayerNorm parameter block
+    int uv;         // columns per column unit: a unit is 16 bytes of a weight row, or 8 bytes in the N = D stages
 };
 
 // One entry of a CTA's copy schedule for a token step.
@@ -79,6 +79,7 @@ struct mg_params {
     int pos0, n_steps;
     uint32_t epoch0;
     int nslot, max_ops, max_cd, res_cap, n_pick_ctas;
+    int S;  // CTAs that share one (sequence, head) in the attention stage, each a slice of the context
     int res_q0, res_nq;  // residual slice = column groups [res_q0, res_q0 + res_nq) of the N=D stages (per CTA: via ops)
     float scale;
 };
@@ -103,7 +104,7 @@ struct rg_mega {
     size_t buf_bytes = 0;
     mg_word* buf_base = nullptr;
     int* d_abort = nullptr;
-    int max_ops = 0, res_cap = 0, n_pick_ctas = 0;
+    int max_ops = 0, res_cap = 0, n_pick_ctas = 0, S = 1;
     int nq_max[3] = {0, 0, 0};  // column groups per op for B = 1, 2, 4
     int nslot = 0;
     size_t smem_bytes = 0;
@@ -155,6 +156,13 @@ __device__ __forceinline__ int mg_ld_flag(const int* p) {
     asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+
+template <typename T>
+__device__ __forceinline__ T mg_from_float(float v);
+template <>
+__device__ __forceinline__ float mg_from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 mg_from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 template <typename T>
 struct mg_vec;
@@ -246,17 +254,18 @@ __device__ void mg_producer(const mg_params& p, const mg_cdesc* cd, int ncd, con
     const size_t rb = (size_t)p.hd * kvsize;
     for (int tok = 0; tok < p.n_steps && !stop; tok++) {
         const int pos = p.pos0 + tok;
-        const int nk = (pos + rc - 1) / rc;
         for (int i = 0; i < ncd && !stop; i++) {
             const mg_cdesc d = cd[i];
-            int nch = 1;
+            int nch = 1, r_lo = 0, arows = 0;
             const unsigned char *kbase = nullptr, *vbase = nullptr;
             if (d.kind == 2) {
                 const mg_op& op = ops[(int)d.src];
                 if (tok > 0) {
-                    const int need = (tok - 1) * nops + (int)d.src;
+                    // cached rows may have been appended by another CTA during the previous token: wait until
+                    // this CTA's consumers have finished that token (they fence after reading its picks)
+                    const int need = tok * nops;
                     uint32_t spins = 0;
-                    while (*s_progress <= need) {
+                    while (*s_progress < need) {
                         if (++spins > MG_SPIN_LIMIT || *s_dead) {
                             stop = true;
                             break;
@@ -265,8 +274,12 @@ __device__ void mg_producer(const mg_params& p, const mg_cdesc* cd, int ncd, con
                     if (stop) break;
                     mg_fence_proxy_async();
                 }
-                nch = 2 * nk;
-                const size_t head_off = (((size_t)op.nq * p.H + op.q0) * p.C) * rb + (size_t)op.layer * p.kv_layer_bytes;
+                const int c = (pos + p.S - 1) / p.S;  // rows per split
+                r_lo = op.aux * c;
+                const int r_hi = min(pos, r_lo + c);
+                arows = max(0, r_hi - r_lo);
+                nch = 2 * ((arows + rc - 1) / rc);
+                const size_t head_off = (((size_t)op.nq * p.H + op.q0) * p.C + r_lo) * rb + (size_t)op.layer * p.kv_layer_bytes;
                 kbase = p.kc + head_off;
                 vbase = p.vc + head_off;
             }
@@ -284,9 +297,9 @@ __device__ void mg_producer(const mg_params& p, const mg_cdesc* cd, int ncd, con
                 if (d.kind == 0) src = p.wpack + d.src, bytes = (uint32_t)d.bytes;
                 else if (d.kind == 1) src = reinterpret_cast<const unsigned char*>(p.lnpack) + d.src, bytes = (uint32_t)d.bytes;
                 else {
-                    const int jj = j < nk ? j : j - nk;
-                    const int rows = min(rc, pos - jj * rc);
-                    src = (j < nk ? kbase : vbase) + (size_t)jj * rc * rb;
+                    const int jj = j >> 1;  // K rows of a range, then V rows of the same range
+                    const int rows = min(rc, arows - jj * rc);
+                    src = ((j & 1) ? vbase : kbase) + (size_t)jj * rc * rb;
                     bytes = (uint32_t)(rows * rb);
                 }
                 mg_mbar_expect_tx(&full[slot], bytes);
@@ -308,72 +321,51 @@ __device__ void mg_producer(const mg_params& p, const mg_cdesc* cd, int ncd, con
     }
 }
 
-// Poll n tagged words (src[i], i < n) until they carry `tag`; payloads to dst[i].
-__device__ __forceinline__ void mg_poll(const mg_word* src, int n, uint32_t tag, float* dst, mg_ctl& ctl) {
-    constexpr int U = 8;
-    for (int base = threadIdx.x; base < n; base += MG_THREADS * U) {
-        mg_word w[U];
+__device__ __forceinline__ void mg_ld_word2(const mg_word* p, mg_word& a, mg_word& b) {
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+
+// Fetch one stage input vector of n values (n even) into dst (shared memory) from
+// tagged words (16-byte aligned), polling until every word carries `tag`.  A thread owns
+// the word pairs tid, tid + 256, ...; one 16-byte load brings a pair (each 8-byte half
+// carries its own tag, so the halves validate independently), up to U loads are issued
+// back to back before any is checked, and only the pairs that were not valid yet are
+// read again, after a short pause that keeps the polling traffic of 148 CTAs off the L2.
+template <int U = 8>
+__device__ __noinline__ void mg_fetch(const mg_word* src, int n, uint32_t tag, float* dst, mg_ctl& ctl) {
+    const int npair = n >> 1;
+    for (int base = threadIdx.x; base < npair; base += MG_THREADS * U) {
+        uint32_t pending = 0;
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (base + u * MG_THREADS < npair) pending |= 1u << u;
         uint32_t spins = 0;
-        bool ok;
-        do {
-            ok = true;
+        while (pending != 0) {
+            mg_word w[U][2];
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                if (pending & (1u << u)) mg_ld_word2(src + 2 * (base + u * MG_THREADS), w[u][0], w[u][1]);
+            uint32_t done = 0;
 #pragma unroll
             for (int u = 0; u < U; u++) {
-                const int i = base + u * MG_THREADS;
-                if (i < n) {
-                    w[u] = mg_ld_word(src + i);
-                    ok = ok && (uint32_t)(w[u] >> 32) == tag;
+                if ((pending & (1u << u)) && (uint32_t)(w[u][0] >> 32) == tag && (uint32_t)(w[u][1] >> 32) == tag) {
+                    const int i = 2 * (base + u * MG_THREADS);
+                    *reinterpret_cast<float2*>(dst + i) =
+                        make_float2(__uint_as_float((uint32_t)w[u][0]), __uint_as_float((uint32_t)w[u][1]));
+                    done |= 1u << u;
                 }
             }
-            if (!ok) {
+            pending &= ~done;
+            if (pending != 0) {
                 if (++spins > MG_SPIN_LIMIT || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
                     mg_give_up(ctl);
                     break;
                 }
+                __nanosleep(64);
             }
-        } while (!ok);
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int i = base + u * MG_THREADS;
-            if (i < n) dst[i] = __uint_as_float((uint32_t)w[u]);
         }
+        if (ctl.dead) break;
     }
-}
-
-// LayerNorm of xr[0..n) in shared memory, in place; gamma/beta in shared memory.
-// Statistics in ONE reduction round: with c = xr[0] as a common shift every thread
-// accumulates sum(x-c) and sum((x-c)^2) over its elements; mean = c + S1/n and the
-// biased variance = S2/n - (S1/n)^2 (eps inside the sqrt, src/ops/norm.rs:41-52).
-// The shift keeps the subtraction well conditioned: (c-mean)^2 <= n*var, so the
-// relative error of the variance stays below n*2^-24.  This is the one-pass idea of
-// fused::layer_norm_fused (src/backend/fused.rs:22-144) in the form that needs a
-// single cross-thread reduction instead of a chain of pairwise Welford merges.
-__device__ void mg_layernorm(float* xr, int n, const float* gamma, const float* beta, float* scratch /* 16 floats */) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const float c = xr[0];
-    float s1 = 0.f, s2 = 0.f;
-    for (int i = tid; i < n; i += MG_THREADS) {
-        const float d = xr[i] - c;
-        s1 += d;
-        s2 = fmaf(d, d, s2);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        s1 += __shfl_xor_sync(RG_FULL_MASK, s1, o);
-        s2 += __shfl_xor_sync(RG_FULL_MASK, s2, o);
-    }
-    if (lane == 0) scratch[warp * 2] = s1, scratch[warp * 2 + 1] = s2;
-    mg_csync();
-    float t1 = 0.f, t2 = 0.f;
-#pragma unroll
-    for (int i = 0; i < MG_THREADS / 32; i++) t1 += scratch[i * 2], t2 += scratch[i * 2 + 1];
-    const float rn = 1.f / (float)n;
-    const float m1 = t1 * rn;
-    const float mean = c + m1;
-    const float var = fmaxf(fmaf(-m1, m1, t2 * rn), 0.f);
-    const float inv = rsqrtf(var + 1e-5f);
-    for (int i = tid; i < n; i += MG_THREADS) xr[i] = (xr[i] - mean) * inv * gamma[i] + beta[i];
-    mg_csync();
 }
 
 __device__ __forceinline__ float mg_block_max(float v, float* scratch) {
@@ -386,21 +378,11 @@ __device__ __forceinline__ float mg_block_max(float v, float* scratch) {
     for (int i = 1; i < MG_THREADS / 32; i++) r = fmaxf(r, scratch[i]);
     return r;
 }
-__device__ __forceinline__ float mg_block_sum(float v, float* scratch) {
-    v = rg_warp_sum(v);
-    mg_csync();
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    mg_csync();
-    float r = 0.f;
-#pragma unroll
-    for (int i = 0; i < MG_THREADS / 32; i++) r += scratch[i];
-    return r;
-}
 
 // Sum N per-lane values across the warp with a halving exchange: while N is even each
 // step sends half of the values to the partner lane and keeps the other half, so N
-// halves per step; the remaining steps are plain butterflies.  On return v[0..N_out)
-// of lane l holds the warp sums of indices base(l) + [0, N_out).
+// halves per step; the remaining steps are plain butterflies.  On return v[0..count)
+// of lane l holds the warp sums of indices base + [0, count).
 template <int N, int O>
 struct mg_halver {
     __device__ __forceinline__ static void run(float (&v)[N], int lane, int& base, int& count) {
@@ -426,16 +408,87 @@ struct mg_halver {
             mg_halver<N, O / 2>::run(v, lane, base, count);
         }
     }
+    // lanes that differ only in bits consumed by plain butterflies hold identical sums: the lowest one writes
+    __device__ __forceinline__ static bool writer(int lane) {
+        int n = N, o = 16;
+        while (o > 0 && n % 2 == 0) n /= 2, o >>= 1;
+        return o == 0 || (lane & (2 * o - 1)) == 0;
+    }
 };
+
+// Dot products of one group (NQA active 16-byte column groups, all K rows) for B input
+// vectors: streams the group's chunks out of the ring, then sums the per-thread partials
+// over the CTA (halving exchange inside a warp, per-warp results to red[warp][value]).
+// Value order: ((q * VEC + j) * B + b).  Returns through t0/t1 the two trailer values of
+// the calling thread's output column (tid < B*NQA*VEC): additive term and LayerNorm
+// mean coefficient.
+template <typename WT, int B, int NQA, int UB, bool TRACE>
+__device__ __forceinline__ void mg_group_dots(const mg_op& op, mg_cons& ring, mg_ctl& ctl, const float* xs, int XLEN,
+                                              float* red, float& t0, float& t1, long long& wait_cyc) {
+    constexpr int UV = UB / (int)sizeof(WT);  // columns per unit
+    constexpr int NV = B * NQA * UV;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float acc[NV];
+#pragma unroll
+    for (int i = 0; i < NV; i++) acc[i] = 0.f;
+    for (int j = 0; j < op.nchunks; j++) {
+        long long c0 = 0;
+        if constexpr (TRACE) c0 = clock64();
+        const unsigned char* slot = mg_ring_wait(ring, ctl);
+        if constexpr (TRACE) wait_cyc += clock64() - c0;
+        const int kb = j * op.kc;
+        const int rows = min(op.kc, op.K - kb);
+        if (j == op.nchunks - 1 && tid < NV) {
+            const float* tr = reinterpret_cast<const float*>(slot + (size_t)NQA * rows * UB);
+            t0 = tr[tid / B];
+            t1 = tr[NQA * UV + tid / B];
+        }
+#pragma unroll 2
+        for (int r = tid; r < rows; r += MG_THREADS) {
+            float xv[B];
+#pragma unroll
+            for (int b = 0; b < B; b++) xv[b] = xs[b * XLEN + kb + r];
+#pragma unroll
+            for (int q = 0; q < NQA; q++) {
+                float w[UV];
+                if constexpr (UB == 16) {
+                    mg_vec<WT>::unpack(*reinterpret_cast<const uint4*>(slot + ((size_t)q * rows + r) * 16), w);
+                } else {
+                    const uint2 v = *reinterpret_cast<const uint2*>(slot + ((size_t)q * rows + r) * 8);
+                    if constexpr (sizeof(WT) == 4) {
+                        w[0] = __uint_as_float(v.x), w[1] = __uint_as_float(v.y);
+                    } else {
+                        w[0] = __uint_as_float(v.x << 16), w[1] = __uint_as_float(v.x & 0xffff0000u);
+                        w[2] = __uint_as_float(v.y << 16), w[3] = __uint_as_float(v.y & 0xffff0000u);
+                    }
+                }
+#pragma unroll
+                for (int jj = 0; jj < UV; jj++)
+#pragma unroll
+                    for (int b = 0; b < B; b++)
+                        acc[(q * UV + jj) * B + b] = fmaf(xv[b], w[jj], acc[(q * UV + jj) * B + b]);
+            }
+        }
+        mg_ring_release(ring);
+    }
+    int base = 0, count = 0;
+    mg_halver<NV, 16>::run(acc, lane, base, count);
+    if (mg_halver<NV, 16>::writer(lane)) {
+#pragma unroll
+        for (int i = 0; i < NV; i++)
+            if (i < count) red[warp * NV + base + i] = acc[i];
+    }
+}
 
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-template <typename WT, int B, int NQ>
+template <typename WT, int B, int NQ, bool TRACE>
 __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(const mg_params p) {
     constexpr int VEC = mg_vec<WT>::N;
     constexpr int KVS = sizeof(WT);  // the KV cache has the weight dtype
-    constexpr int NOUT = B * NQ * VEC;  // finished values per group
+    constexpr int NOUT = B * NQ * VEC;  // most finished values a group can have
+    constexpr int NWARP = MG_THREADS / 32;
     static_assert(NOUT <= MG_THREADS, "one thread per finished value");
     extern __shared__ __align__(128) unsigned char smem_raw[];
 
@@ -456,18 +509,22 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
     sp += (size_t)p.max_cd * sizeof(mg_cdesc);
     float* xs = reinterpret_cast<float*>(sp);  // [B][XLEN] input vector of the current stage
     sp += (size_t)B * XLEN * 4;
-    float* xres = reinterpret_cast<float*>(sp);  // [B][res_cap] this CTA's slice of the residual stream
-    sp += (size_t)B * p.res_cap * 4;
-    float* sc = reinterpret_cast<float*>(sp);  // [C] attention scores / probabilities
-    sp += (size_t)p.C * 4;
+    float* xemb = reinterpret_cast<float*>(sp);  // [B][D] token + position embedding of the step
+    sp += (size_t)B * p.D * 4;
     float* go = reinterpret_cast<float*>(sp);  // [MG_THREADS * VEC] attention output partials
     sp += (size_t)MG_THREADS * VEC * 4;
-    float* sqkv = reinterpret_cast<float*>(sp);  // q, k, v of the new row: 3 * hd
+    // xs, xemb and go are contiguous: the out-projection stage, which needs neither xemb nor go, lays the
+    // attention records of all heads and its own input vectors over the three of them
+    float* xres = reinterpret_cast<float*>(sp);  // [B][res_cap] this CTA's slice of the residual stream
+    sp += (size_t)B * p.res_cap * 4;
+    float* gml = reinterpret_cast<float*>(sp);  // [2][64] attention partial max / sum
+    sp += 128 * 4;
+    float* sqkv = reinterpret_cast<float*>(sp);  // q, k, v of the new row: 3 * 128
     sp += 3 * 128 * 4;
     float* red = reinterpret_cast<float*>(sp);  // [8][NOUT]
-    sp += 8 * NOUT * 4;
-    float* scratch = reinterpret_cast<float*>(sp);  // 32 floats
-    sp += 32 * 4;
+    sp += NWARP * NOUT * 4;
+    float* scratch = reinterpret_cast<float*>(sp);  // [8][2][B] LayerNorm partial sums
+    sp += NWARP * 2 * MG_BMAX * 4;
     float* bestv = reinterpret_cast<float*>(sp);  // [NOUT]
     sp += NOUT * 4;
     int* besti = reinterpret_cast<int*>(sp);  // [NOUT]
@@ -488,13 +545,13 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
     for (int i = tid; i < ncd * (int)(sizeof(mg_cdesc) / 4); i += MG_TOTAL_THREADS)
         reinterpret_cast<int*>(cds)[i] = reinterpret_cast<const int*>(p.cds + cd0)[i];
     if (tid == 0) {
-        for (int i = 0; i < p.nslot; i++) mg_mbar_init(&full[i], 1), mg_mbar_init(&empty[i], MG_THREADS / 32);
+        for (int i = 0; i < p.nslot; i++) mg_mbar_init(&full[i], 1), mg_mbar_init(&empty[i], NWARP);
         s_flags[0] = -1, s_flags[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    if (warp == MG_THREADS / 32) {
+    if (warp == NWARP) {
         // =================== producer warp ===================
         if (lane == 0)
             mg_producer(p, cds, ncd, ops, nops, slots, full, empty, p.nslot, s_flags, s_flags + 1, KVS);
@@ -516,9 +573,13 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
     int res_q0 = 0, res_n = 0;
     for (int i = 0; i < nops; i++)
         if (ops[i].type == MG_OPROJ && ops[i].layer == 0) {
-            if (res_n == 0) res_q0 = ops[i].q0;
-            res_n += ops[i].nq * VEC;
+            if (res_n == 0) res_q0 = ops[i].q0 * ops[i].uv;  // first column of the slice
+            res_n += ops[i].nq * ops[i].uv;
         }
+    bool stats_pending = false;
+    float mu[B], rstd[B];  // LayerNorm statistics of the current stage's input
+#pragma unroll
+    for (int b = 0; b < B; b++) mu[b] = 0.f, rstd[b] = 1.f;
 
     for (int t = 0; t < p.n_steps && !ctl.dead; t++) {
         const int pos = p.pos0 + t;
@@ -528,14 +589,14 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
         for (int b = 0; b < B; b++) {
             const uint32_t tok = t == 0 ? p.tokens[(size_t)b * p.C + pos] : s_pick[b];
             for (int k = tid; k < p.D; k += MG_THREADS)
-                xs[b * XLEN + k] = rg_to_float(wte[(size_t)tok * p.ldt + k]) + rg_to_float(wpe[(size_t)pos * p.ldt + k]);
+                xemb[b * p.D + k] = rg_to_float(wte[(size_t)tok * p.ldt + k]) + rg_to_float(wpe[(size_t)pos * p.ldt + k]);
         }
         mg_csync();
         for (int i = tid; i < B * res_n; i += MG_THREADS) {
             const int b = i / res_n, j = i - b * res_n;
-            xres[b * p.res_cap + j] = xs[b * XLEN + res_q0 * VEC + j];
+            xres[b * p.res_cap + j] = xemb[b * p.D + res_q0 + j];
         }
-        // thread-local best logit of the head stage (thread tid < NOUT serves sequence tid / (NQ*VEC))
+        // thread-local best logit of the head stage (thread tid serves sequence tid % B)
         float my_best = -INFINITY;
         int my_besti = 0x7fffffff;
 
@@ -547,25 +608,26 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
             if (tid == 0) *reinterpret_cast<volatile int*>(s_flags) = t * nops + oi;  // the producer reads this
             const mg_op op = ops[oi];
             const uint32_t tag = tagbase + (uint32_t)op.layer + 1u;
-            const bool tracing = p.trace != nullptr && t == p.n_steps - 1 && tid == 0;
+            const bool tracing = TRACE && p.trace != nullptr && t == p.n_steps - 1 && tid == 0;
             unsigned long long* tr = tracing ? p.trace + ((size_t)cta * p.max_ops + oi) * 8 : nullptr;
             long long wait_cyc = 0, poll_cyc = 0;
             if (tracing) tr[0] = mg_globaltimer();
-            auto timed_wait = [&]() -> const unsigned char* {
-                const long long c0 = clock64();
-                const unsigned char* sl = mg_ring_wait(ring, ctl);
-                wait_cyc += clock64() - c0;
-                return sl;
-            };
 
             if (op.type == MG_ATTN) {
                 // =================== attention of (sequence b, head h) ===================
-                const int b = op.nq, h = op.q0, HD = p.hd;
-                const int LPR = HD / VEC;            // lanes per cached row
-                const int RPP = MG_THREADS / LPR;    // rows per pass of the CTA
-                const int sub = tid % LPR, grp = tid / LPR;
-                // q, k, v of the new row from the QKV stage
-                for (int i = tid; i < 3 * HD; i += MG_THREADS) {
+                // One CTA per (sequence, head).  Each warp owns every 8th group of cached rows and keeps its
+                // own running softmax (max m, sum l, output o); K rows and V rows of the same positions arrive
+                // as consecutive chunks.  The partials of all warps and the new row are merged at the end:
+                // exactly softmax(q.K^T * scale).V with the row maximum subtracted (src/nn/attention.rs:78-94).
+                const int b = op.nq, h = op.q0, HD = p.hd, S = p.S, sidx = op.aux;
+                const int LPR = HD / VEC;   // lanes per cached row
+                const int RPW = 32 / LPR;   // rows per warp per pass
+                const int sub = lane % LPR, g2 = lane / LPR;
+                const bool is_last = sidx == S - 1;  // this CTA also takes the new row and appends it to the cache
+                const int csz = (pos + S - 1) / S;
+                const int r_lo = sidx * csz;
+                const int arows = max(0, min(pos, r_lo + csz) - r_lo);  // cached rows of this CTA's slice
+                for (int i = tid; i < (is_last ? 3 : 1) * HD; i += MG_THREADS) {
                     const int which = i / HD, d = i - which * HD;
                     const mg_word* src = p.buf_qkv + (size_t)b * 3 * p.D + which * p.D + h * HD + d;
                     uint32_t spins = 0;
@@ -582,100 +644,117 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                     sqkv[which * 128 + d] = v;
                 }
                 mg_csync();
-                const int rc = mg_attn_rows_per_chunk(HD, KVS);
-                const int nk = (pos + rc - 1) / rc;
+                const int rc = mg_attn_rows_per_chunk(HD, KVS);  // = 8 passes of the 8 warps
+                const int nk = (arows + rc - 1) / rc;
                 if (tracing) tr[1] = mg_globaltimer();
                 float qf[VEC];
 #pragma unroll
                 for (int j = 0; j < VEC; j++) qf[j] = sqkv[sub * VEC + j];
-                // ---- scores: S = (q . k) * scale (src/nn/attention.rs:78-87); 4 rows per thread in flight ----
-                float mx = -INFINITY;
+                float m = -INFINITY, l = 0.f, acc[VEC];
+#pragma unroll
+                for (int j = 0; j < VEC; j++) acc[j] = 0.f;
                 for (int j = 0; j < nk; j++) {
-                    const unsigned char* slot = timed_wait();
-                    const int rows = min(rc, pos - j * rc);
-                    for (int r0 = 0; r0 < rows; r0 += 4 * RPP) {
-                        float dot[4];
+                    const int rows = min(rc, arows - j * rc);
+                    float sreg[8];
+                    {   // scores of this warp's rows of the chunk: 8 independent rows in flight per lane group.
+                        // Rows past the end are read from the last valid row and masked: no branches.
+                        long long c0 = 0;
+                        if constexpr (TRACE) c0 = clock64();
+                        const unsigned char* slot = mg_ring_wait(ring, ctl);
+                        if constexpr (TRACE) wait_cyc += clock64() - c0;
 #pragma unroll
-                        for (int u = 0; u < 4; u++) {
-                            const int rr = r0 + u * RPP + grp;
-                            dot[u] = 0.f;
-                            if (rr < rows) {
-                                float kf[VEC];
-                                mg_vec<WT>::unpack(*reinterpret_cast<const uint4*>(slot + ((size_t)rr * LPR + sub) * 16), kf);
+                        for (int u = 0; u < 8; u++) {
+                            const int rr = min((u * NWARP + warp) * RPW + g2, rows - 1);
+                            float kf[VEC];
+                            mg_vec<WT>::unpack(*reinterpret_cast<const uint4*>(slot + ((size_t)rr * LPR + sub) * 16), kf);
+                            float dot = 0.f;
 #pragma unroll
-                                for (int jj = 0; jj < VEC; jj++) dot[u] = fmaf(qf[jj], kf[jj], dot[u]);
-                            }
+                            for (int jj = 0; jj < VEC; jj++) dot = fmaf(qf[jj], kf[jj], dot);
+                            sreg[u] = dot;
                         }
                         for (int o = LPR >> 1; o > 0; o >>= 1) {
 #pragma unroll
-                            for (int u = 0; u < 4; u++) dot[u] += __shfl_xor_sync(RG_FULL_MASK, dot[u], o);
+                            for (int u = 0; u < 8; u++) sreg[u] += __shfl_xor_sync(RG_FULL_MASK, sreg[u], o);
                         }
-#pragma unroll
-                        for (int u = 0; u < 4; u++) {
-                            const int rr = r0 + u * RPP + grp;
-                            if (rr < rows) {
-                                const float sv = dot[u] * p.scale;
-                                mx = fmaxf(mx, sv);
-                                if (sub == 0) sc[j * rc + rr] = sv;
-                            }
-                        }
+                        mg_ring_release(ring);
                     }
-                    mg_ring_release(ring);
+                    float cm = -INFINITY;
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int rr = (u * NWARP + warp) * RPW + g2;
+                        sreg[u] = rr < rows ? sreg[u] * p.scale : -INFINITY;
+                        cm = fmaxf(cm, sreg[u]);
+                    }
+                    const float mn = fmaxf(m, cm);
+                    const float msafe = mn == -INFINITY ? 0.f : mn;  // a group that has seen no row yet
+                    const float corr = __expf(m - msafe);            // exp(-inf) = 0 while m is still -inf
+                    m = mn;
+                    float psum = 0.f;
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        sreg[u] = __expf(sreg[u] - msafe);  // masked rows: exp(-inf) = 0
+                        psum += sreg[u];
+                    }
+                    l = l * corr + psum;
+#pragma unroll
+                    for (int jj = 0; jj < VEC; jj++) acc[jj] *= corr;
+                    {
+                        long long c0 = 0;
+                        if constexpr (TRACE) c0 = clock64();
+                        const unsigned char* slot = mg_ring_wait(ring, ctl);
+                        if constexpr (TRACE) wait_cyc += clock64() - c0;
+#pragma unroll
+                        for (int u = 0; u < 8; u++) {
+                            const int rr = min((u * NWARP + warp) * RPW + g2, rows - 1);
+                            float vf[VEC];
+                            mg_vec<WT>::unpack(*reinterpret_cast<const uint4*>(slot + ((size_t)rr * LPR + sub) * 16), vf);
+#pragma unroll
+                            for (int jj = 0; jj < VEC; jj++) acc[jj] = fmaf(sreg[u], vf[jj], acc[jj]);
+                        }
+                        mg_ring_release(ring);
+                    }
                 }
-                {   // the new row's score, by every warp for itself (cheap, saves a barrier)
+                // the new row's score (every warp computes it: cheaper than sharing it)
+                float s_new = -INFINITY;
+                if (is_last) {
                     float dot = 0.f;
                     for (int d = lane; d < HD; d += 32) dot = fmaf(sqkv[d], sqkv[128 + d], dot);
-                    dot = rg_warp_sum(dot) * p.scale;
-                    mx = fmaxf(mx, dot);
-                    if (tid == 0) sc[pos] = dot;
+                    s_new = rg_warp_sum(dot) * p.scale;
                 }
-                // ---- softmax over positions 0..pos (max-subtracted, src/ops/elementwise.rs:144-157) ----
-                mx = mg_block_max(mx, scratch);  // its barriers also publish sc[]
-                float sum = 0.f;
-                for (int i = tid; i <= pos; i += MG_THREADS) {
-                    const float e = __expf(sc[i] - mx);
-                    sc[i] = e;
-                    sum += e;
-                }
-                sum = mg_block_sum(sum, scratch);
+                const int grp = warp * RPW + g2;  // partial index, NWARP * RPW of them
+                if (sub == 0) gml[grp] = m, gml[64 + grp] = l;
+#pragma unroll
+                for (int j = 0; j < VEC; j++) go[grp * HD + sub * VEC + j] = acc[j];
                 if (tracing) tr[2] = mg_globaltimer();
-                // ---- output: P . v, two independent accumulators per thread ----
-                float acc[2][VEC];
-#pragma unroll
-                for (int j = 0; j < VEC; j++) acc[0][j] = 0.f, acc[1][j] = 0.f;
-                if (grp == 0) {
-                    const float pn = sc[pos];
-#pragma unroll
-                    for (int j = 0; j < VEC; j++) acc[0][j] = pn * sqkv[256 + sub * VEC + j];
-                }
-                for (int j = 0; j < nk; j++) {
-                    const unsigned char* slot = timed_wait();
-                    const int rows = min(rc, pos - j * rc);
-                    for (int r0 = grp; r0 < rows; r0 += 2 * RPP) {
-#pragma unroll
-                        for (int u = 0; u < 2; u++) {
-                            const int rr = r0 + u * RPP;
-                            if (rr < rows) {
-                                float vf[VEC];
-                                mg_vec<WT>::unpack(*reinterpret_cast<const uint4*>(slot + ((size_t)rr * LPR + sub) * 16), vf);
-                                const float pr = sc[j * rc + rr];
-#pragma unroll
-                                for (int jj = 0; jj < VEC; jj++) acc[u][jj] = fmaf(pr, vf[jj], acc[u][jj]);
-                            }
-                        }
-                    }
-                    mg_ring_release(ring);
-                }
-#pragma unroll
-                for (int j = 0; j < VEC; j++) go[grp * HD + sub * VEC + j] = acc[0][j] + acc[1][j];
                 mg_csync();
                 if (tid < HD) {
-                    float o0 = 0.f, o1 = 0.f;
-                    for (int g2 = 0; g2 < RPP; g2 += 2) o0 += go[g2 * HD + tid], o1 += go[(g2 + 1) * HD + tid];
-                    mg_st_word(p.buf_a + (size_t)b * p.D + h * HD + tid, tag, __float_as_uint(__fdividef(o0 + o1, sum)));
+                    // this CTA's record: running max, sum and un-normalised output over its slice (+ the new row)
+                    const int ng = NWARP * RPW;
+                    float M = s_new;
+                    for (int g = 0; g < ng; g++) M = fmaxf(M, gml[g]);
+                    float num = 0.f, den = 0.f;
+                    if (M != -INFINITY) {
+                        if (is_last) {
+                            const float wn = __expf(s_new - M);
+                            num = wn * sqkv[256 + tid], den = wn;
+                        }
+                        for (int g = 0; g < ng; g++) {
+                            const float w = __expf(gml[g] - M);  // 0 for a group that saw no row
+                            num = fmaf(w, go[g * HD + tid], num);
+                            den = fmaf(w, gml[64 + g], den);
+                        }
+                    }
+                    mg_word* rec = p.buf_a + (((size_t)b * p.H + h) * S + sidx) * (HD + 2);
+                    mg_st_word(rec + 2 + tid, tag, __float_as_uint(num));
+                    if (tid == 0) {
+                        mg_st_word(rec, tag, __float_as_uint(M));
+                        mg_st_word(rec + 1, tag, __float_as_uint(den));
+                    }
                 }
-                {   // append k, v at row pos, off the critical path (generic-proxy stores; later tokens read them
-                    // with bulk copies, which the producer issues only after this op is over)
+                if (is_last) {
+                    // append k, v at row pos, off the critical path.  Generic-proxy stores that later tokens read
+                    // with bulk copies, possibly from another CTA: proxy fence + gpu-scope fence here, and every
+                    // CTA fences again after it has read the token's picks (which depend on this CTA's later stores).
                     const size_t row = (((size_t)b * p.H + h) * p.C + pos) * HD;
                     WT* kdst = reinterpret_cast<WT*>(p.kc + (size_t)op.layer * p.kv_layer_bytes) + row;
                     WT* vdst = reinterpret_cast<WT*>(p.vc + (size_t)op.layer * p.kv_layer_bytes) + row;
@@ -687,103 +766,146 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                         else reinterpret_cast<__nv_bfloat16*>(dst)[d] = __float2bfloat16_rn(v);
                     }
                     mg_fence_proxy_async();
+                    __threadfence();
                 }
                 if (tracing) tr[3] = mg_globaltimer(), tr[4] = (unsigned long long)wait_cyc, tr[5] = 0;
                 continue;
             }
 
             // =================== projection stages ===================
+            const bool ln_stage = op.type == MG_QKV || op.type == MG_FC1 || op.type == MG_HEAD;
             if (op.flags & MG_FIRST) {
-                // the stage's input vector, complete, into xs
+                // the stage's input vector, complete, into xs.  For a LayerNorm stage the packed weights already
+                // hold g_k W_kn; mean and 1/sqrt(var + eps) are applied to the finished dot products:
+                //   LN(x).W + b = rstd * (sum_k x_k g_k W_kn - mean * sum_k g_k W_kn) + (sum_k beta_k W_kn + b_n)
+                // (the two column sums are precomputed at load time and ride at the end of the group's weights).
                 const mg_word* src =
                     op.type == MG_OPROJ ? p.buf_a : (op.type == MG_FC1 ? p.buf_xc : (op.type == MG_FC2 ? p.buf_h : p.buf_xe));
                 const int n_in = op.type == MG_FC2 ? p.F : p.D;
                 const uint32_t in_tag = (op.type == MG_QKV || op.type == MG_HEAD) ? tag - 1u : tag;  // previous block's output
-                const long long c0 = clock64();
-                if (!(op.type == MG_QKV && op.layer == 0))  // block 0 starts from the embedding already in xs
-                    for (int b = 0; b < B; b++) mg_poll(src + (size_t)b * n_in, n_in, in_tag, xs + b * XLEN, ctl);
-                mg_csync();
-                poll_cyc += clock64() - c0;
-                if (op.flags & MG_LNPRE) {
-                    const float* gb = reinterpret_cast<const float*>(timed_wait());
-                    for (int b = 0; b < B; b++) mg_layernorm(xs + b * XLEN, p.D, gb, gb + p.D, scratch);
-                    mg_ring_release(ring);
-                }
-            }
-            if (tracing) tr[1] = mg_globaltimer();
-            // ---- dot products of this group's columns over all K rows ----
-            float acc[NOUT];
+                const bool local = op.type == MG_QKV && op.layer == 0;  // block 0 starts from the embedding
+                long long c0 = 0;
+                if constexpr (TRACE) c0 = clock64();
+                if (ln_stage) {
+                    // raw vector in (gamma is already folded into the packed weights); the thread's partial sums
+                    // go to scratch and are combined in the epilogue, after the barrier that follows the dot products
 #pragma unroll
-            for (int i = 0; i < NOUT; i++) acc[i] = 0.f;
-            float bias_v = 0.f;
-            for (int j = 0; j < op.nchunks; j++) {
-                const unsigned char* slot = timed_wait();
-                const int kb = j * op.kc;
-                const int rows = min(op.kc, op.K - kb);
-                if (j == op.nchunks - 1 && tid < NOUT) {
-                    const int jq = tid % (NQ * VEC);
-                    if (jq < op.nq * VEC) bias_v = reinterpret_cast<const float*>(slot + (size_t)op.nq * rows * 16)[jq];
-                }
-#pragma unroll 2
-                for (int r = tid; r < rows; r += MG_THREADS) {
-                    float xv[B];
-#pragma unroll
-                    for (int b = 0; b < B; b++) xv[b] = xs[b * XLEN + kb + r];
-#pragma unroll
-                    for (int q = 0; q < NQ; q++) {
-                        if (q < op.nq) {
-                            float w[VEC];
-                            mg_vec<WT>::unpack(*reinterpret_cast<const uint4*>(slot + ((size_t)q * rows + r) * 16), w);
-#pragma unroll
-                            for (int b = 0; b < B; b++)
-#pragma unroll
-                                for (int jj = 0; jj < VEC; jj++)
-                                    acc[(b * NQ + q) * VEC + jj] = fmaf(xv[b], w[jj], acc[(b * NQ + q) * VEC + jj]);
+                    for (int b = 0; b < B; b++) {
+                        if (local) {
+                            for (int i = tid; i < n_in; i += MG_THREADS) xs[b * XLEN + i] = xemb[b * p.D + i];
+                        } else {
+                            mg_fetch<8>(src + (size_t)b * n_in, n_in, in_tag, xs + b * XLEN, ctl);
                         }
                     }
+                    mg_csync();
+#pragma unroll
+                    for (int b = 0; b < B; b++) {
+                        const float* xr = xs + b * XLEN;
+                        const float c = xr[0];
+                        float s1 = 0.f, s2 = 0.f;
+                        for (int i = tid; i < n_in; i += MG_THREADS) {
+                            const float d = xr[i] - c;
+                            s1 += d;
+                            s2 = fmaf(d, d, s2);
+                        }
+                        s1 = rg_warp_sum(s1);
+                        s2 = rg_warp_sum(s2);
+                        if (lane == 0) scratch[(warp * 2) * B + b] = s1, scratch[(warp * 2 + 1) * B + b] = s2;
+                    }
+                    stats_pending = true;
+                } else if (op.type == MG_OPROJ) {
+                    // attention records of every (sequence, head, slice) -> merged, normalised head outputs
+                    const int rec = p.hd + 2, nrec = B * p.H * p.S * rec;
+                    mg_fetch<8>(p.buf_a, nrec, in_tag, xs, ctl);
+                    mg_csync();
+                    float* vec = xs + ((nrec + 3) & ~3);
+                    for (int i = tid; i < B * p.D; i += MG_THREADS) {
+                        const int b = i / p.D, k = i - b * p.D;
+                        const int hh = k / p.hd, d = k - hh * p.hd;
+                        const float* r0 = xs + ((size_t)(b * p.H + hh) * p.S) * rec;
+                        float M = -INFINITY;
+                        for (int sp2 = 0; sp2 < p.S; sp2++) M = fmaxf(M, r0[sp2 * rec]);
+                        float num = 0.f, den = 0.f;
+                        for (int sp2 = 0; sp2 < p.S; sp2++) {
+                            const float w = __expf(r0[sp2 * rec] - M);  // 0 for an empty slice (its max is -inf)
+                            num = fmaf(w, r0[sp2 * rec + 2 + d], num);
+                            den = fmaf(w, r0[sp2 * rec + 1], den);
+                        }
+                        vec[i] = __fdividef(num, den);
+                    }
+                    mg_csync();
+                } else {
+#pragma unroll
+                    for (int b = 0; b < B; b++) mg_fetch<8>(src + (size_t)b * n_in, n_in, in_tag, xs + b * XLEN, ctl);
+                    mg_csync();
                 }
-                mg_ring_release(ring);
+                if constexpr (TRACE) poll_cyc += clock64() - c0;
             }
-            // ---- sum over the 256 threads: halving exchange inside a warp, fixed order across warps ----
-            {
-                int base = 0, count = 0;
-                mg_halver<NOUT, 16>::run(acc, lane, base, count);
-                // lanes that differ only in the bits consumed by plain butterflies hold the same sums: the lowest writes
-                bool writer = true;
-                {
-                    int n = NOUT, o = 16;
-                    while (o > 0 && n % 2 == 0) n /= 2, o >>= 1;
-                    if (o > 0) writer = (lane & (2 * o - 1)) == 0;
+            if (tracing) tr[1] = mg_globaltimer();
+            // ---- dot products of this group's columns over all K rows, summed over the CTA ----
+            float t0 = 0.f, t1 = 0.f;
+            const float* xin = xs;
+            int xstride = XLEN;
+            if (op.type == MG_OPROJ) xin = xs + ((B * p.H * p.S * (p.hd + 2) + 3) & ~3), xstride = p.D;
+            if (op.uv == VEC) {
+                switch (op.nq) {
+                    case 1: mg_group_dots<WT, B, 1, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                    case 2: if constexpr (NQ >= 2) mg_group_dots<WT, B, 2, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                    case 3: if constexpr (NQ >= 3) mg_group_dots<WT, B, 3, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                    case 4: if constexpr (NQ >= 4) mg_group_dots<WT, B, 4, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                    case 5: if constexpr (NQ >= 5) mg_group_dots<WT, B, 5, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                    default: if constexpr (NQ >= 6) mg_group_dots<WT, B, 6, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
                 }
-                if (writer)
-                    for (int i = 0; i < count; i++) red[warp * NOUT + base + i] = acc[i];
+            } else {  // 8-byte units (N = D stages): half as many columns per unit, twice as many units allowed
+                switch (op.nq) {
+                    case 1: mg_group_dots<WT, B, 1, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                    case 2: mg_group_dots<WT, B, 2, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                    case 3: if constexpr (NQ >= 2) mg_group_dots<WT, B, 3, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                    case 4: if constexpr (NQ >= 2) mg_group_dots<WT, B, 4, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                    case 5: if constexpr (NQ >= 3) mg_group_dots<WT, B, 5, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                    default: if constexpr (NQ >= 3) mg_group_dots<WT, B, 6, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                }
             }
             mg_csync();
-            if (tracing) tr[2] = mg_globaltimer();
-            if (tid < NOUT) {
-                const int b = tid / (NQ * VEC), jq = tid - b * (NQ * VEC);
-                if (jq < op.nq * VEC) {
-                    float s = bias_v;
+            if (stats_pending) {
+                // shifted sums of all warps -> mean and 1/sqrt(biased variance + eps) (src/ops/norm.rs:41-52)
 #pragma unroll
-                    for (int w2 = 0; w2 < MG_THREADS / 32; w2++) s += red[w2 * NOUT + tid];
-                    const int col = op.q0 * VEC + jq;
-                    if (op.type == MG_QKV) {
-                        mg_st_word(p.buf_qkv + (size_t)b * 3 * p.D + col, tag, __float_as_uint(s));
-                    } else if (op.type == MG_OPROJ) {
-                        const float v = xres[b * p.res_cap + op.aux + jq] + s;
-                        xres[b * p.res_cap + op.aux + jq] = v;
-                        mg_st_word(p.buf_xc + (size_t)b * p.D + col, tag, __float_as_uint(v));
-                    } else if (op.type == MG_FC1) {
-                        const float v = rg_apply_act(s, p.act);
-                        mg_st_word(p.buf_h + (size_t)b * p.F + col, tag, __float_as_uint(v));
-                    } else if (op.type == MG_FC2) {
-                        const float v = xres[b * p.res_cap + op.aux + jq] + s;
-                        xres[b * p.res_cap + op.aux + jq] = v;
-                        mg_st_word(p.buf_xe + (size_t)b * p.D + col, tag, __float_as_uint(v));
-                    } else if (col < p.V) {  // MG_HEAD
-                        p.logits[(size_t)b * p.V + col] = s;
-                        if (s > my_best || (s == my_best && col < my_besti)) my_best = s, my_besti = col;
-                    }
+                for (int b = 0; b < B; b++) {
+                    float t1s = 0.f, t2s = 0.f;
+#pragma unroll
+                    for (int w2 = 0; w2 < NWARP; w2++) t1s += scratch[(w2 * 2) * B + b], t2s += scratch[(w2 * 2 + 1) * B + b];
+                    const float rn = 1.f / (float)p.D;
+                    const float m1 = t1s * rn;
+                    mu[b] = xs[b * XLEN] + m1;
+                    rstd[b] = rsqrtf(fmaxf(fmaf(-m1, m1, t2s * rn), 0.f) + 1e-5f);
+                }
+                stats_pending = false;
+            }
+            if (tracing) tr[2] = mg_globaltimer();
+            const int nv = B * op.nq * op.uv;
+            if (tid < nv) {
+                const int b = tid % B, jq = tid / B;
+                float s = 0.f;
+#pragma unroll
+                for (int w2 = 0; w2 < NWARP; w2++) s += red[w2 * nv + tid];
+                s = ln_stage ? fmaf(rstd[b], fmaf(-mu[b], t1, s), t0) : s + t0;
+                const int col = op.q0 * op.uv + jq;
+                if (op.type == MG_QKV) {
+                    mg_st_word(p.buf_qkv + (size_t)b * 3 * p.D + col, tag, __float_as_uint(s));
+                } else if (op.type == MG_OPROJ) {
+                    const float v = xres[b * p.res_cap + op.aux + jq] + s;
+                    xres[b * p.res_cap + op.aux + jq] = v;
+                    mg_st_word(p.buf_xc + (size_t)b * p.D + col, tag, __float_as_uint(v));
+                } else if (op.type == MG_FC1) {
+                    const float v = rg_apply_act(s, p.act);
+                    mg_st_word(p.buf_h + (size_t)b * p.F + col, tag, __float_as_uint(v));
+                } else if (op.type == MG_FC2) {
+                    const float v = xres[b * p.res_cap + op.aux + jq] + s;
+                    xres[b * p.res_cap + op.aux + jq] = v;
+                    mg_st_word(p.buf_xe + (size_t)b * p.D + col, tag, __float_as_uint(v));
+                } else if (col < p.V) {  // MG_HEAD
+                    p.logits[(size_t)b * p.V + col] = s;
+                    if (s > my_best || (s == my_best && col < my_besti)) my_best = s, my_besti = col;
                 }
             }
             if (tracing) tr[3] = mg_globaltimer(), tr[4] = (unsigned long long)wait_cyc, tr[5] = (unsigned long long)poll_cyc;
@@ -794,9 +916,9 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                 if (tid < B) {
                     float bv = -INFINITY;
                     int bi = 0x7fffffff;
-                    for (int i = 0; i < NQ * VEC; i++) {
-                        const float v = bestv[tid * NQ * VEC + i];
-                        const int ix = besti[tid * NQ * VEC + i];
+                    for (int i = tid; i < NOUT; i += B) {  // thread i served sequence i % B
+                        const float v = bestv[i];
+                        const int ix = besti[i];
                         if (v > bv || (v == bv && ix < bi)) bv = v, bi = ix;
                     }
                     mg_word* dst = p.buf_pick + ((size_t)op.aux * B + tid) * 2;
@@ -808,7 +930,10 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
         if (ctl.dead) break;
 
         // ---- greedy pick (top_k = 1 of src/wasm_api.rs:120-156): best over all CTAs, lowest index on ties ----
-        mg_poll(p.buf_pick, p.n_pick_ctas * B * 2, tagbase + (uint32_t)p.L + 1u, pickbuf, ctl);
+        mg_fetch<8>(p.buf_pick, p.n_pick_ctas * B * 2, tagbase + (uint32_t)p.L + 1u, pickbuf, ctl);
+        // everything any CTA stored before its pick (cache rows included) is ordered before what follows here
+        __threadfence();
+        mg_fence_proxy_async();
         mg_csync();
         if (warp < B) {  // warp b scans the candidates of sequence b
             float bv = -INFINITY;
@@ -853,6 +978,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
 // ---------------------------------------------------------------------------
 template <typename WT>
 static __global__ void mg_pack_kernel(const WT* __restrict__ W, long long ldw, const float* __restrict__ bias, int N,
+                                      const float* __restrict__ gamma, const float* __restrict__ beta,
                                       const mg_op* __restrict__ ops, const int* __restrict__ cta_off, int type, int layer,
                                       unsigned char* __restrict__ dst) {
     constexpr int VEC = 16 / sizeof(WT);
@@ -861,18 +987,31 @@ static __global__ void mg_pack_kernel(const WT* __restrict__ W, long long ldw, c
         const mg_op op = ops[oi];
         if (op.type != type || op.layer != layer) continue;
         const int total = op.nq * op.K;
+        const int UB = op.uv * (int)sizeof(WT);  // 16 or 8 bytes per unit and row
         for (int e = threadIdx.x; e < total; e += blockDim.x) {
             const int k = e / op.nq, q = e - k * op.nq;
             const int j = k / op.kc, r = k - j * op.kc;
             const int rows = min(op.kc, op.K - j * op.kc);
-            const uint4 v = *reinterpret_cast<const uint4*>(W + (size_t)k * ldw + (size_t)(op.q0 + q) * VEC);
-            *reinterpret_cast<uint4*>(dst + op.src + ((size_t)j * op.nq * op.kc + (size_t)q * rows + r) * 16) = v;
+            const WT* srcp = W + (size_t)k * ldw + (size_t)(op.q0 + q) * op.uv;
+            WT* dstp = reinterpret_cast<WT*>(dst + op.src + ((size_t)j * op.nq * op.kc + (size_t)q * rows + r) * UB);
+            const float gk = gamma != nullptr ? gamma[k] : 1.f;  // LayerNorm stage: store gamma_k * W_kn (exact when gamma is 1)
+            for (int i = 0; i < op.uv; i++) dstp[i] = gamma != nullptr ? mg_from_float<WT>(gk * rg_to_float(srcp[i])) : srcp[i];
         }
-        // trailer of the last chunk: the f32 bias of the group's columns
-        float* tail = reinterpret_cast<float*>(dst + op.src + (size_t)op.nq * op.K * 16);
-        for (int e = threadIdx.x; e < op.nq * VEC; e += blockDim.x) {
-            const int col = op.q0 * VEC + e;
-            tail[e] = col < N ? bias[col] : 0.f;
+        // trailer of the last chunk, per column of the group: [additive term][mean coefficient].
+        // plain stage: bias, 0.  LayerNorm stage: sum_k beta_k W_kn + bias_n, sum_k gamma_k W_kn.
+        float* tail = reinterpret_cast<float*>(dst + op.src + (size_t)op.nq * op.K * UB);
+        for (int e = threadIdx.x; e < op.nq * op.uv; e += blockDim.x) {
+            const int col = op.q0 * op.uv + e;
+            float add = col < N ? bias[col] : 0.f, coef = 0.f;
+            if (gamma != nullptr && col < N) {
+                for (int k = 0; k < op.K; k++) {
+                    const float w = rg_to_float(W[(size_t)k * ldw + col]);
+                    add = fmaf(beta[k], w, add);
+                    coef += rg_to_float(mg_from_float<WT>(gamma[k] * w));  // the folded weight as stored
+                }
+            }
+            tail[e] = add;
+            tail[op.nq * op.uv + e] = coef;
         }
     }
 }
@@ -900,8 +1039,8 @@ static size_t mg_smem_bytes(const rg_gpt* m, int B, int NQ, int nslot, int max_o
     const int VEC = m->bf16 ? 8 : 4;
     const int NOUT = B * NQ * VEC;
     size_t s = (size_t)nslot * MG_SLOT_BYTES + 128 + (size_t)max_ops * sizeof(mg_op) + (size_t)max_cd * sizeof(mg_cdesc);
-    s += (size_t)B * m->F * 4 + (size_t)B * res_cap * 4 + (size_t)m->C * 4 + (size_t)MG_THREADS * VEC * 4 + 3 * 128 * 4;
-    s += 8 * (size_t)NOUT * 4 + 32 * 4 + 2 * (size_t)NOUT * 4 + MG_BMAX * 4 + 16 + (size_t)n_pick * B * 2 * 4;
+    s += (size_t)B * m->F * 4 + (size_t)B * m->D * 4 + (size_t)B * res_cap * 4 + (size_t)MG_THREADS * VEC * 4 + 128 * 4 + 3 * 128 * 4;
+    s += 8 * (size_t)NOUT * 4 + 8 * 2 * MG_BMAX * 4 + 2 * (size_t)NOUT * 4 + MG_BMAX * 4 + 16 + (size_t)n_pick * B * 2 * 4;
     return s + 128;
 }
 
@@ -909,9 +1048,17 @@ static size_t mg_smem_bytes(const rg_gpt* m, int B, int NQ, int nslot, int max_o
 static void mg_build_program(rg_gpt* m, rg_mega* g, int B) {
     const int G = g->G, VEC = m->bf16 ? 8 : 4, NQ = mg_nq_for(m->bf16, B);
     std::vector<std::vector<mg_op>> per(G);
+    // slices of the context per (sequence, head): as many as there are CTAs for, at most 4, and only as many as
+    // let the out-projection stage hold all attention records plus its input vectors in the xs/xemb/go overlay
+    g->S = std::max(1, std::min(4, G / std::max(1, B * m->H)));
+    while (g->S > 1 && (size_t)B * m->H * g->S * (m->hd + 2) + 4 + (size_t)B * m->D >
+                           (size_t)B * m->F + (size_t)B * m->D + (size_t)MG_THREADS * VEC)
+        g->S--;
     int rot = 0;
-    auto add_projection = [&](int type, int layer, int K, int N, int fixed_rot, int ln_off) {
-        const int Q = rg_cdiv(N, VEC);
+    auto add_projection = [&](int type, int layer, int K, int N, int fixed_rot, int ub) {
+        const int UV = ub / (int)m->wsize;         // columns per unit
+        const int NQU = ub == 16 ? NQ : std::min(6, 2 * NQ);  // units per op
+        const int Q = rg_cdiv(N, UV);
         const int base = Q / G, extra = Q % G;
         const int r0 = fixed_rot >= 0 ? fixed_rot : rot;
         const int active = std::min(G, Q);
@@ -925,20 +1072,19 @@ static void mg_build_program(rg_gpt* m, rg_mega* g, int B) {
                 mg_op op;
                 memset(&op, 0, sizeof(op));
                 op.type = type, op.layer = layer, op.K = K;
-                op.nq = std::min(nq, NQ), op.q0 = q;
-                const size_t budget = MG_SLOT_BYTES - 256;  // room for the bias trailer of the last chunk
-                const size_t bytes = (size_t)op.nq * K * 16;
+                op.nq = std::min(nq, NQU), op.q0 = q, op.uv = UV;
+                const size_t budget = MG_SLOT_BYTES - 256;  // room for the trailer of the last chunk
+                const size_t bytes = (size_t)op.nq * K * ub;
                 const int nch = (int)((bytes + budget - 1) / budget);
                 int kc = rg_cdiv(K, nch);
                 kc = (kc + 31) / 32 * 32;
-                while ((size_t)op.nq * kc * 16 > budget) kc -= 32;
+                while ((size_t)op.nq * kc * ub > budget) kc -= 32;
                 op.kc = std::max(kc, 1);
                 op.nchunks = rg_cdiv(K, op.kc);
                 op.flags = first ? MG_FIRST : 0;
-                if (first && ln_off >= 0) op.flags |= MG_LNPRE, op.ln_off = ln_off;
                 op.aux = type == MG_HEAD ? r : aux;
                 first = false;
-                aux += op.nq * VEC;
+                aux += op.nq * UV;
                 q += op.nq, nq -= op.nq;
                 if (nq == 0) op.flags |= MG_LAST;
                 per[c].push_back(op);
@@ -947,22 +1093,23 @@ static void mg_build_program(rg_gpt* m, rg_mega* g, int B) {
         if (fixed_rot < 0) rot = (rot + extra) % G;
         return active;
     };
-    const int extraD = rg_cdiv(m->D, VEC) % G;
+    const int extraD = rg_cdiv(m->D, VEC / 2) % G;
     rot = extraD;  // stages with N != D put their larger shares on other CTAs than the N = D stages do
     for (int l = 0; l < m->L; l++) {
-        add_projection(MG_QKV, l, m->D, 3 * m->D, -1, (4 * l) * m->D);
-        for (int pr = 0; pr < B * m->H; pr++) {  // one CTA per (sequence, head), from the top of the grid down
+        add_projection(MG_QKV, l, m->D, 3 * m->D, -1, 16);
+        for (int pr = 0; pr < B * m->H * g->S; pr++) {  // one CTA per (sequence, head, slice), from the top of the grid down
             mg_op op;
             memset(&op, 0, sizeof(op));
-            op.type = MG_ATTN, op.layer = l, op.nq = pr / m->H, op.q0 = pr % m->H;
+            const int bh = pr / g->S;
+            op.type = MG_ATTN, op.layer = l, op.nq = bh / m->H, op.q0 = bh % m->H, op.aux = pr % g->S, op.K = g->S;
             op.flags = MG_FIRST | MG_LAST;
             per[(G - 1) - (pr % G)].push_back(op);
         }
-        add_projection(MG_OPROJ, l, m->D, m->D, 0, -1);
-        add_projection(MG_FC1, l, m->D, m->F, -1, (4 * l + 2) * m->D);
-        add_projection(MG_FC2, l, m->F, m->D, 0, -1);
+        add_projection(MG_OPROJ, l, m->D, m->D, 0, 8);
+        add_projection(MG_FC1, l, m->D, m->F, -1, 16);
+        add_projection(MG_FC2, l, m->F, m->D, 0, 8);
     }
-    g->n_pick_ctas = add_projection(MG_HEAD, m->L, m->D, m->V, -1, (4 * m->L) * m->D);
+    g->n_pick_ctas = add_projection(MG_HEAD, m->L, m->D, m->V, -1, 16);
     g->ops.clear();
     g->cta_off.assign(G + 1, 0);
     g->max_ops = 1;
@@ -974,9 +1121,10 @@ static void mg_build_program(rg_gpt* m, rg_mega* g, int B) {
         for (mg_op& op : per[c]) {
             if (op.type != MG_ATTN) {
                 op.src = (long long)off;
-                off += (size_t)op.nq * op.K * 16 + (size_t)op.nq * VEC * 4;
+                off += (size_t)op.nq * op.K * op.uv * m->wsize + 2 * (size_t)op.nq * op.uv * 4;
+                off = (off + 15) & ~(size_t)15;
             }
-            if (op.type == MG_OPROJ && op.layer == 0) res += op.nq * VEC;
+            if (op.type == MG_OPROJ && op.layer == 0) res += op.nq * op.uv;
             g->ops.push_back(op);
         }
         g->max_ops = std::max(g->max_ops, (int)per[c].size());
@@ -996,12 +1144,13 @@ static void mg_build_program(rg_gpt* m, rg_mega* g, int B) {
                 g->cds.push_back({(long long)(oi - g->cta_off[c]), 0, 2});
                 continue;
             }
-            if (op.flags & MG_LNPRE) g->cds.push_back({(long long)op.ln_off * 4, 2 * m->D * 4, 1});
             for (int j = 0; j < op.nchunks; j++) {
                 const int rows = std::min(op.kc, op.K - j * op.kc);
-                int bytes = op.nq * rows * 16;
-                if (j == op.nchunks - 1) bytes += op.nq * VEC * 4;
-                g->cds.push_back({op.src + (long long)j * op.nq * op.kc * 16, bytes, 0});
+                const int ub = op.uv * (int)m->wsize;
+                int bytes = op.nq * rows * ub;
+                if (j == op.nchunks - 1) bytes += 2 * op.nq * op.uv * 4;  // trailer
+                bytes = (bytes + 15) & ~15;
+                g->cds.push_back({op.src + (long long)j * op.nq * op.kc * ub, bytes, 0});
             }
         }
         g->max_cd = std::max(g->max_cd, (int)g->cds.size() - g->cd_off[c]);
@@ -1016,30 +1165,37 @@ static void mg_pack_all(rg_gpt* m, rg_mega* g) {
         rg_layer& y = m->layers[l];
         const rg_linear* lins[4] = {&y.qkv, &y.o, &y.fc1, &y.fc2};
         const int types[4] = {MG_QKV, MG_OPROJ, MG_FC1, MG_FC2};
+        const float* gam[4] = {y.ln1g, nullptr, y.ln2g, nullptr};
+        const float* bet[4] = {y.ln1b, nullptr, y.ln2b, nullptr};
         for (int i = 0; i < 4; i++)
-            mg_pack_kernel<WT><<<g->G, 256, 0, s>>>((const WT*)lins[i]->W, lins[i]->ldw, lins[i]->b, lins[i]->N, g->d_ops,
-                                                    g->d_cta_off, types[i], l, g->d_wpack);
+            mg_pack_kernel<WT><<<g->G, 256, 0, s>>>((const WT*)lins[i]->W, lins[i]->ldw, lins[i]->b, lins[i]->N, gam[i], bet[i],
+                                                    g->d_ops, g->d_cta_off, types[i], l, g->d_wpack);
         float* ln = g->d_lnpack + (size_t)4 * l * m->D;
         cudaMemcpyAsync(ln, y.ln1g, m->D * 4, cudaMemcpyDeviceToDevice, s);
         cudaMemcpyAsync(ln + m->D, y.ln1b, m->D * 4, cudaMemcpyDeviceToDevice, s);
         cudaMemcpyAsync(ln + 2 * m->D, y.ln2g, m->D * 4, cudaMemcpyDeviceToDevice, s);
         cudaMemcpyAsync(ln + 3 * m->D, y.ln2b, m->D * 4, cudaMemcpyDeviceToDevice, s);
     }
-    mg_pack_kernel<WT><<<g->G, 256, 0, s>>>((const WT*)m->head.W, m->head.ldw, m->head.b, m->head.N, g->d_ops, g->d_cta_off,
-                                            MG_HEAD, m->L, g->d_wpack);
+    mg_pack_kernel<WT><<<g->G, 256, 0, s>>>((const WT*)m->head.W, m->head.ldw, m->head.b, m->head.N, m->lnfg, m->lnfb, g->d_ops,
+                                            g->d_cta_off, MG_HEAD, m->L, g->d_wpack);
     float* lnf = g->d_lnpack + (size_t)4 * m->L * m->D;
     cudaMemcpyAsync(lnf, m->lnfg, m->D * 4, cudaMemcpyDeviceToDevice, s);
     cudaMemcpyAsync(lnf + m->D, m->lnfb, m->D * 4, cudaMemcpyDeviceToDevice, s);
     m->ctx->launches += 4 * m->L + 1;
 }
 
-template <typename WT, int B, int NQ>
-static cudaError_t mg_launch(rg_gpt* m, rg_mega* g, mg_params& prm) {
-    auto kern = rg_token_loop_kernel<WT, B, NQ>;
+template <typename WT, int B, int NQ, bool TRACE>
+static cudaError_t mg_launch_t(rg_gpt* m, rg_mega* g, mg_params& prm) {
+    auto kern = rg_token_loop_kernel<WT, B, NQ, TRACE>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g->smem_bytes);
     if (e != cudaSuccess) return e;
     void* args[] = {&prm};
     return cudaLaunchCooperativeKernel((void*)kern, dim3(g->G), dim3(MG_TOTAL_THREADS), args, g->smem_bytes, m->ctx->stream);
+}
+
+template <typename WT, int B, int NQ>
+static cudaError_t mg_launch(rg_gpt* m, rg_mega* g, mg_params& prm) {
+    return prm.trace ? mg_launch_t<WT, B, NQ, true>(m, g, prm) : mg_launch_t<WT, B, NQ, false>(m, g, prm);
 }
 
 // (Re)build program, packed weights and exchange buffers for batch B.
@@ -1072,12 +1228,13 @@ static rg_status mg_prepare(rg_gpt* m, int B) {
     RG_TRY(mg_dalloc(g, (void**)&g->d_trace, (size_t)g->G * g->max_ops * 8 * 8));
     RG_CUDA(cudaMemset(g->d_trace, 0, (size_t)g->G * g->max_ops * 8 * 8));
     RG_TRY(mg_dalloc(g, (void**)&g->d_abort, 16));
-    const size_t words = (size_t)B * (3 * m->D + m->D + m->D + m->F + m->D) + (size_t)g->n_pick_ctas * B * 2;
+    const size_t arec_words = (size_t)B * m->H * g->S * (m->hd + 2);
+    const size_t words = (size_t)B * (3 * m->D + m->D + m->F + m->D) + arec_words + (size_t)g->n_pick_ctas * B * 2;
     RG_TRY(mg_dalloc(g, (void**)&g->buf_base, words * 8));
     g->buf_bytes = words * 8;
     mg_word* w = g->buf_base;
     g->buf_qkv = w, w += (size_t)B * 3 * m->D;
-    g->buf_a = w, w += (size_t)B * m->D;
+    g->buf_a = w, w += arec_words;
     g->buf_xc = w, w += (size_t)B * m->D;
     g->buf_h = w, w += (size_t)B * m->F;
     g->buf_xe = w, w += (size_t)B * m->D;
@@ -1147,6 +1304,7 @@ rg_status rg_mega_run(rg_gpt* m, int B, size_t pos0, size_t n_steps) {
     prm.V = m->V, prm.D = m->D, prm.L = m->L, prm.H = m->H, prm.hd = m->hd, prm.C = m->C, prm.F = m->F;
     prm.act = m->cfg.activation;
     prm.pos0 = (int)pos0, prm.n_steps = (int)n_steps, prm.epoch0 = m->epoch;
+    prm.S = g->S;
     prm.nslot = g->nslot, prm.max_ops = g->max_ops, prm.res_cap = g->res_cap, prm.n_pick_ctas = g->n_pick_ctas;
     prm.scale = 1.f / sqrtf((float)m->hd);
     cudaError_t e;
