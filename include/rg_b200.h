@@ -128,6 +128,8 @@ typedef struct rg_gpt_config {
     int activation;    /* RG_ACT_RELU (src/nn/feedforward.rs:43-45) or RG_ACT_GELU_TANH (src/backend/fused.rs:151-175) */
     int weight_dtype;  /* RG_DTYPE_F32, or RG_DTYPE_BF16: matrices, tables and KV cache kept in bf16 */
     size_t max_batch;  /* sequences the KV cache is sized for */
+    int tp_rank;       /* tensor parallelism: this process's rank ... */
+    int tp_size;       /* ... of tp_size (0 or 1 = none).  One process and one GPU per rank. */
 } rg_gpt_config;
 
 /* GPTModel::new(config), src/models/gpt.rs:27-54 (asserts embedding_dim % num_heads == 0, src/nn/attention.rs:38-41) */
@@ -172,6 +174,16 @@ RG_API rg_status rg_gpt_reset(rg_gpt* m);
 /* Algorithmic bytes one decode step reads at context length T for B sequences
  * (weights + biases + LN + one table row pair + K/V of every cached position). */
 RG_API double rg_gpt_decode_step_bytes(const rg_gpt* m, size_t B, double mean_ctx);
+
+/* Tensor parallelism (nothing to mirror: the reference has no multi-device path).  With
+ * cfg.tp_size > 1 every rank creates the same model with its own tp_rank, loads the SAME full
+ * parameter list (it keeps only its shard: heads of Wq/Wk/Wv and the matching rows of Wo, columns
+ * of W1 with the matching rows of W2, a vocabulary slice of the LM head) and joins one NCCL
+ * communicator: rank 0 calls rg_gpt_tp_unique_id, the 128 bytes travel to the other ranks by any
+ * host channel, then every rank calls rg_gpt_tp_init (collective).  Each block then costs two
+ * all-reduces of [B, embedding_dim] over NVLink, the head one all-gather of logits. */
+RG_API rg_status rg_gpt_tp_unique_id(uint8_t id_out[128]);
+RG_API rg_status rg_gpt_tp_init(rg_gpt* m, const uint8_t id[128]);
 
 /* Profiling aid of the persistent token-loop kernel (engine-only, nothing to mirror in the
  * reference): when enabled, the last token step of every rg_gpt_decode_run records device

@@ -57,7 +57,8 @@ _ERRORS = {c.status: c for c in (ShapeError, DimensionError, InvalidInput, Backe
 class GptConfigC(C.Structure):
     _fields_ = [("block_size", C.c_size_t), ("vocab_size", C.c_size_t), ("num_layers", C.c_size_t),
                 ("num_heads", C.c_size_t), ("embedding_dim", C.c_size_t), ("causal", C.c_int),
-                ("activation", C.c_int), ("weight_dtype", C.c_int), ("max_batch", C.c_size_t)]
+                ("activation", C.c_int), ("weight_dtype", C.c_int), ("max_batch", C.c_size_t),
+                ("tp_rank", C.c_int), ("tp_size", C.c_int)]
 
 
 _P = C.c_void_p
@@ -117,6 +118,8 @@ SIGNATURES = {
     "rg_gpt_position": (C.c_size_t, [_P]),
     "rg_gpt_reset": (None, [_P]),
     "rg_gpt_decode_step_bytes": (C.c_double, [_P, _SZ, C.c_double]),
+    "rg_gpt_tp_unique_id": (None, [C.POINTER(C.c_uint8)]),
+    "rg_gpt_tp_init": (None, [_P, C.POINTER(C.c_uint8)]),
     "rg_gpt_trace_enable": (None, [_P, C.c_int]),
     "rg_gpt_trace_read": (None, [_P, C.POINTER(C.c_uint64), _SZ, _SZP]),
     "rg_linear_row_noalloc": (None, [_P, _P, _P, _P, _SZ, _SZ, _P]),

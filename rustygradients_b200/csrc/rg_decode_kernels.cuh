@@ -388,7 +388,7 @@ static __global__ void __launch_bounds__(1024) rg_pick_kernel(rg_pick_args p) {
     int besti = 0x7fffffff;
     const size_t stride = (size_t)p.B * p.V;
     for (int v = tid; v < p.V; v += blockDim.x) {
-        float x = p.bias[v];
+        float x = p.bias ? p.bias[v] : 0.f;
         const float* pp = p.parts + (size_t)b * p.V + v;
         for (int s = 0; s < p.nparts; s++) x += pp[s * stride];
         p.logits[(size_t)b * p.V + v] = x;

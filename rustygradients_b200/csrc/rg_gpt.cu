@@ -13,6 +13,74 @@
 
 #include <algorithm>
 
+#include <dlfcn.h>
+#include <nccl.h>  // types and prototypes only: the library is resolved at run time
+
+// ---------------------------------------------------------------------------
+// tensor parallelism: NCCL resolved with dlopen (the process normally has it loaded already)
+// ---------------------------------------------------------------------------
+struct rg_nccl_api {
+    decltype(&ncclGetUniqueId) GetUniqueId = nullptr;
+    decltype(&ncclCommInitRank) CommInitRank = nullptr;
+    decltype(&ncclCommDestroy) CommDestroy = nullptr;
+    decltype(&ncclAllReduce) AllReduce = nullptr;
+    decltype(&ncclAllGather) AllGather = nullptr;
+    decltype(&ncclGetErrorString) GetErrorString = nullptr;
+    bool ok = false;
+};
+static rg_nccl_api g_nccl;
+static rg_status load_nccl() {
+    if (g_nccl.ok) return RG_OK;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return rg_fail(RG_ERR_BACKEND, "tensor parallelism needs NCCL: cannot load libnccl.so.2 (%s)", dlerror());
+#define RG_SYM(name)                                                          \
+    g_nccl.name = reinterpret_cast<decltype(g_nccl.name)>(dlsym(h, "nccl" #name)); \
+    if (!g_nccl.name) return rg_fail(RG_ERR_BACKEND, "libnccl has no symbol nccl" #name);
+    RG_SYM(GetUniqueId) RG_SYM(CommInitRank) RG_SYM(CommDestroy) RG_SYM(AllReduce) RG_SYM(AllGather) RG_SYM(GetErrorString)
+#undef RG_SYM
+    g_nccl.ok = true;
+    return RG_OK;
+}
+#define RG_NCCL(expr)                                                                                      \
+    do {                                                                                                   \
+        ncclResult_t _r = (expr);                                                                          \
+        if (_r != ncclSuccess)                                                                             \
+            return rg_fail(RG_ERR_BACKEND, "NCCL error %d (%s) at %s:%d", (int)_r, g_nccl.GetErrorString(_r), \
+                           __FILE__, __LINE__);                                                            \
+    } while (0)
+
+// out[i] = sum over the k-splits of parts[s][i] (+ bias[i % n_bias]), fixed order
+// (rows of n_bias values each; out row stride ld_out, 0 = contiguous)
+static __global__ void rg_reduce_parts_kernel(const float* __restrict__ parts, int nparts, size_t n,
+                                              const float* __restrict__ bias, int n_bias, float* __restrict__ out,
+                                              long long ld_out = 0) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = bias ? bias[i % n_bias] : 0.f;
+    for (int s = 0; s < nparts; s++) v += parts[(size_t)s * n + i];
+    if (ld_out) out[(i / n_bias) * ld_out + i % n_bias] = v;
+    else out[i] = v;
+}
+// x[m][n] += t[m][n] + bias[n]
+static __global__ void rg_add_bias_res_kernel(float* __restrict__ x, const float* __restrict__ t,
+                                              const float* __restrict__ bias, size_t rows, int N) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * N) return;
+    x[i] += t[i] + bias[i % N];
+}
+// gathered [ranks][rows][Vpad] -> logits [rows][V]
+static __global__ void rg_ungather_logits_kernel(const float* __restrict__ g, float* __restrict__ logits, size_t rows, int V,
+                                                 int Vpad) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * V) return;
+    const size_t r = i / V;
+    const int v = (int)(i - r * V);
+    const int rank = v / Vpad;
+    logits[i] = g[((size_t)rank * rows + r) * Vpad + (v - rank * Vpad)];
+}
+
 static __global__ void rg_set_int2_kernel(int* a, int* b, int v) {
     *a = v;
     if (b) *b = v;
@@ -95,6 +163,29 @@ extern "C" rg_status rg_gpt_create(rg_ctx* ctx, const rg_gpt_config* cfg, rg_gpt
     m->bf16 = cfg->weight_dtype == RG_DTYPE_BF16;
     m->wsize = m->bf16 ? 2 : 4;
     m->ldt = round_up(m->D, 8);
+    m->tp_size = std::max(1, cfg->tp_size), m->tp_rank = cfg->tp_size > 1 ? cfg->tp_rank : 0;
+    if (m->tp_rank < 0 || m->tp_rank >= m->tp_size || m->tp_size > m->H) {
+        const int r = m->tp_rank, t = m->tp_size;
+        delete m;
+        return rg_fail(RG_ERR_INVALID_INPUT, "tp_rank %d / tp_size %d not usable with %zu heads", r, t, cfg->num_heads);
+    }
+    {   // shard of this rank: whole heads, hidden columns in multiples of 8, one block of the vocabulary
+        const int T = m->tp_size, r = m->tp_rank;
+        m->Hl = m->H / T + (r < m->H % T ? 1 : 0);
+        m->h0 = r * (m->H / T) + std::min(r, m->H % T);
+        m->Dl = m->Hl * m->hd;
+        const int F8 = m->F / 8;
+        m->Fl = 8 * (F8 / T + (r < F8 % T ? 1 : 0));
+        m->f0 = 8 * (r * (F8 / T) + std::min(r, F8 % T));
+        m->Vpad = (int)round_up(rg_cdiv(m->V, T), 8);
+        m->v0 = std::min(m->V, r * m->Vpad);
+        m->Vl = std::max(0, std::min(m->Vpad, m->V - m->v0));
+        if (T == 1) m->Vpad = m->V;
+        if (m->Vl == 0) {
+            delete m;
+            return rg_fail(RG_ERR_INVALID_INPUT, "tp_size %d leaves rank %d without vocabulary", T, r);
+        }
+    }
     const char* ng = getenv("RG_B200_NO_GRAPH");
     m->use_graph = !(ng && ng[0] == '1');
 
@@ -109,25 +200,30 @@ extern "C" rg_status rg_gpt_create(rg_ctx* ctx, const rg_gpt_config* cfg, rg_gpt
     m->layers.resize(m->L);
     for (int l = 0; l < m->L && st == RG_OK; l++) {
         rg_layer& y = m->layers[l];
-        TRY(alloc_linear(m, y.qkv, m->D, 3 * m->D));
-        TRY(alloc_linear(m, y.o, m->D, m->D));
-        TRY(alloc_linear(m, y.fc1, m->D, m->F));
-        TRY(alloc_linear(m, y.fc2, m->F, m->D));
+        TRY(alloc_linear(m, y.qkv, m->D, 3 * m->Dl));
+        TRY(alloc_linear(m, y.o, m->Dl, m->D));
+        TRY(alloc_linear(m, y.fc1, m->D, m->Fl));
+        TRY(alloc_linear(m, y.fc2, m->Fl, m->D));
         TRY(dalloc(m, (void**)&y.ln1g, m->D * 4));
         TRY(dalloc(m, (void**)&y.ln1b, m->D * 4));
         TRY(dalloc(m, (void**)&y.ln2g, m->D * 4));
         TRY(dalloc(m, (void**)&y.ln2b, m->D * 4));
     }
-    if (st == RG_OK) TRY(alloc_linear(m, m->head, m->D, m->V));
+    if (st == RG_OK) TRY(alloc_linear(m, m->head, m->D, m->Vl));
     const size_t kvsize = m->bf16 ? 2 : 4;
-    m->kv_layer_bytes = (size_t)m->Bmax * m->H * m->C * m->hd * kvsize;
+    m->kv_layer_bytes = (size_t)m->Bmax * m->Hl * m->C * m->hd * kvsize;
     TRY(dalloc(m, (void**)&m->kc, m->kv_layer_bytes * m->L));
     TRY(dalloc(m, (void**)&m->vc, m->kv_layer_bytes * m->L));
     // split of the context across CTAs in the token-step attention
-    m->NS = std::max(1, std::min(16, rg_cdiv(ctx->sm_count, m->H)));
+    m->NS = std::max(1, std::min(16, rg_cdiv(ctx->sm_count, m->Hl)));
     TRY(dalloc(m, (void**)&m->xa, (size_t)m->Bmax * m->D * 4));
     TRY(dalloc(m, (void**)&m->xb, (size_t)m->Bmax * m->D * 4));
-    TRY(dalloc(m, (void**)&m->ap, (size_t)m->Bmax * m->H * m->NS * (m->hd + 2) * 4));
+    TRY(dalloc(m, (void**)&m->ap, (size_t)m->Bmax * m->Hl * m->NS * (m->hd + 2) * 4));
+    if (m->tp_size > 1) {
+        TRY(dalloc(m, (void**)&m->tp_vec, (size_t)m->Bmax * m->D * 4));
+        TRY(dalloc(m, (void**)&m->tp_local, (size_t)m->Bmax * m->Vpad * 4));
+        TRY(dalloc(m, (void**)&m->tp_gather, (size_t)m->tp_size * m->Bmax * m->Vpad * 4));
+    }
     TRY(dalloc(m, (void**)&m->logits, (size_t)m->Bmax * m->V * 4));
     TRY(dalloc(m, (void**)&m->tokens, (size_t)m->Bmax * m->C * 4));
     TRY(dalloc(m, (void**)&m->picks, (size_t)m->Bmax * 4));
@@ -164,6 +260,7 @@ extern "C" rg_status rg_gpt_destroy(rg_gpt* m) {
     cudaSetDevice(m->ctx->device);
     cudaStreamSynchronize(m->ctx->stream);
     if (m->graph) cudaGraphExecDestroy(m->graph);
+    if (m->nccl_comm && g_nccl.ok) g_nccl.CommDestroy((ncclComm_t)m->nccl_comm);
     rg_mega_destroy(m);
     for (void* p : m->allocs) cudaFree(p);
     delete m;
@@ -210,13 +307,17 @@ static inline uint16_t f32_to_bf16_rne(float f) {
 
 // Copy a row-major [rows][cols] f32 host matrix into columns [col0, col0+cols) of a
 // device matrix with leading dimension ld, converting to the weight dtype.
-static rg_status upload_matrix(rg_gpt* m, void* dst, long long ld, int col0, const float* src, int rows, int cols) {
+// The host block is rows x cols at src (row stride src_ld floats).
+static rg_status upload_matrix(rg_gpt* m, void* dst, long long ld, int col0, const float* src, int rows, int cols,
+                               long long src_ld = -1) {
+    if (src_ld < 0) src_ld = cols;
     if (!m->bf16) {
-        RG_CUDA(cudaMemcpy2D((float*)dst + col0, ld * 4, src, (size_t)cols * 4, (size_t)cols * 4, rows,
+        RG_CUDA(cudaMemcpy2D((float*)dst + col0, ld * 4, src, (size_t)src_ld * 4, (size_t)cols * 4, rows,
                              cudaMemcpyHostToDevice));
     } else {
         std::vector<uint16_t> tmp((size_t)rows * cols);
-        for (size_t i = 0; i < tmp.size(); i++) tmp[i] = f32_to_bf16_rne(src[i]);
+        for (int r = 0; r < rows; r++)
+            for (int c = 0; c < cols; c++) tmp[(size_t)r * cols + c] = f32_to_bf16_rne(src[(size_t)r * src_ld + c]);
         RG_CUDA(cudaMemcpy2D((uint16_t*)dst + col0, ld * 2, tmp.data(), (size_t)cols * 2, (size_t)cols * 2, rows,
                              cudaMemcpyHostToDevice));
     }
@@ -249,25 +350,26 @@ extern "C" rg_status rg_gpt_load_params(rg_gpt* m, const float* const* data, con
     for (int l = 0; l < m->L; l++) {
         const float* const* p = data + 2 + 16 * l;
         rg_layer& y = m->layers[l];
-        for (int j = 0; j < 3; j++) {  // Wq | Wk | Wv side by side: one [D,3D] projection
-            RG_TRY(upload_matrix(m, y.qkv.W, y.qkv.ldw, j * D, p[2 * j], D, D));
-            RG_TRY(upload_vec(y.qkv.b + j * D, p[2 * j + 1], D));
+        const int Dl = m->Dl, c0 = m->h0 * m->hd;  // this rank's heads = columns [c0, c0 + Dl) of Wq, Wk, Wv
+        for (int j = 0; j < 3; j++) {  // Wq | Wk | Wv side by side: one [D, 3 Dl] projection
+            RG_TRY(upload_matrix(m, y.qkv.W, y.qkv.ldw, j * Dl, p[2 * j] + c0, D, Dl, D));
+            RG_TRY(upload_vec(y.qkv.b + j * Dl, p[2 * j + 1] + c0, Dl));
         }
-        RG_TRY(upload_matrix(m, y.o.W, y.o.ldw, 0, p[6], D, D));
+        RG_TRY(upload_matrix(m, y.o.W, y.o.ldw, 0, p[6] + (size_t)c0 * D, Dl, D, D));  // rows of Wo for the same heads
         RG_TRY(upload_vec(y.o.b, p[7], D));
         RG_TRY(upload_vec(y.ln1g, p[8], D));
         RG_TRY(upload_vec(y.ln1b, p[9], D));
-        RG_TRY(upload_matrix(m, y.fc1.W, y.fc1.ldw, 0, p[10], D, F));
-        RG_TRY(upload_vec(y.fc1.b, p[11], F));
-        RG_TRY(upload_matrix(m, y.fc2.W, y.fc2.ldw, 0, p[12], F, D));
+        RG_TRY(upload_matrix(m, y.fc1.W, y.fc1.ldw, 0, p[10] + m->f0, D, m->Fl, F));  // hidden columns [f0, f0 + Fl)
+        RG_TRY(upload_vec(y.fc1.b, p[11] + m->f0, m->Fl));
+        RG_TRY(upload_matrix(m, y.fc2.W, y.fc2.ldw, 0, p[12] + (size_t)m->f0 * D, m->Fl, D, D));  // and the matching rows
         RG_TRY(upload_vec(y.fc2.b, p[13], D));
         RG_TRY(upload_vec(y.ln2g, p[14], D));
         RG_TRY(upload_vec(y.ln2b, p[15], D));
     }
     RG_TRY(upload_vec(m->lnfg, data[n - 4], D));
     RG_TRY(upload_vec(m->lnfb, data[n - 3], D));
-    RG_TRY(upload_matrix(m, m->head.W, m->head.ldw, 0, data[n - 2], D, V));
-    RG_TRY(upload_vec(m->head.b, data[n - 1], V));
+    RG_TRY(upload_matrix(m, m->head.W, m->head.ldw, 0, data[n - 2] + m->v0, D, m->Vl, V));  // vocabulary slice
+    RG_TRY(upload_vec(m->head.b, data[n - 1] + m->v0, m->Vl));
     m->loaded = true;
     m->pos = 0;
     m->curB = 0;
@@ -281,26 +383,45 @@ static rg_status ensure_rows(rg_gpt* m, size_t rows) {
     if (rows <= m->rowsCap) return RG_OK;
     RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
     dfree(m, m->px), dfree(m, m->pln), dfree(m, m->pqkv), dfree(m, m->pattn), dfree(m, m->ph), dfree(m, m->plast);
-    m->px = m->pln = m->pqkv = m->pattn = m->ph = m->plast = nullptr;
+    dfree(m, m->ptp);
+    m->px = m->pln = m->pqkv = m->pattn = m->ph = m->plast = m->ptp = nullptr;
     m->rowsCap = 0;
     RG_TRY(dalloc(m, (void**)&m->px, rows * m->D * 4));
     RG_TRY(dalloc(m, (void**)&m->pln, rows * m->D * 4));
-    RG_TRY(dalloc(m, (void**)&m->pqkv, rows * 3 * m->D * 4));
-    RG_TRY(dalloc(m, (void**)&m->pattn, rows * m->D * 4));
-    RG_TRY(dalloc(m, (void**)&m->ph, rows * m->F * 4));
+    RG_TRY(dalloc(m, (void**)&m->pqkv, rows * 3 * m->Dl * 4));
+    RG_TRY(dalloc(m, (void**)&m->pattn, rows * m->Dl * 4));
+    RG_TRY(dalloc(m, (void**)&m->ph, rows * m->Fl * 4));
+    if (m->tp_size > 1) RG_TRY(dalloc(m, (void**)&m->ptp, rows * m->D * 4));
     RG_TRY(dalloc(m, (void**)&m->plast, (size_t)m->Bmax * m->D * 4));
     m->rowsCap = rows;
     return RG_OK;
 }
 
-static rg_status gemm(rg_gpt* m, const float* A, int M, const rg_linear& lin, float* Cout, const float* res, int act) {
+static rg_status tp_ready(rg_gpt* m) {
+    if (m->tp_size > 1 && !m->nccl_comm)
+        return rg_fail(RG_ERR_INVALID_INPUT, "tensor-parallel model: call rg_gpt_tp_init on every rank first");
+    return RG_OK;
+}
+static rg_status tp_allreduce(rg_gpt* m, float* buf, size_t n) {
+    RG_NCCL(g_nccl.AllReduce(buf, buf, n, ncclFloat32, ncclSum, (ncclComm_t)m->nccl_comm, m->ctx->stream));
+    RG_LAUNCHED(m->ctx);
+    return RG_OK;
+}
+static rg_status tp_allgather(rg_gpt* m, const float* send, float* recv, size_t n_per_rank) {
+    RG_NCCL(g_nccl.AllGather(send, recv, n_per_rank, ncclFloat32, (ncclComm_t)m->nccl_comm, m->ctx->stream));
+    RG_LAUNCHED(m->ctx);
+    return RG_OK;
+}
+
+static rg_status gemm(rg_gpt* m, const float* A, int M, const rg_linear& lin, float* Cout, const float* res, int act,
+                      bool with_bias = true, long long ldc = -1) {
     rg_gemm_args p;
     memset(&p, 0, sizeof(p));
     p.A = A, p.lda = lin.K;
     p.W = lin.W, p.ldw = lin.ldw;
-    p.C = Cout, p.ldc = lin.N;
+    p.C = Cout, p.ldc = ldc < 0 ? lin.N : ldc;
     p.M = M, p.N = lin.N, p.K = lin.K;
-    p.bias = lin.b, p.res = res, p.ldres = lin.N, p.act = act;
+    p.bias = with_bias ? lin.b : nullptr, p.res = res, p.ldres = lin.N, p.act = act;
     if (m->bf16) RG_CUDA(rg_gemm_launch<__nv_bfloat16>(m->ctx->stream, p, 1));
     else RG_CUDA(rg_gemm_launch<float>(m->ctx->stream, p, 1));
     RG_LAUNCHED(m->ctx);
@@ -312,18 +433,50 @@ static rg_status attn_rows(rg_gpt* m, int l, int B, int T) {
     const KT* kc = (const KT*)(m->kc + (size_t)l * m->kv_layer_bytes);
     const KT* vc = (const KT*)(m->vc + (size_t)l * m->kv_layer_bytes);
     cudaStream_t s = m->ctx->stream;
-    rg_kv_scatter_kernel<KT><<<B * T, 256, 0, s>>>(m->pqkv, (KT*)kc, (KT*)vc, T, m->H, m->hd, m->C, m->D);
-    dim3 grid(rg_cdiv(T, 8), m->H, B);
+    rg_kv_scatter_kernel<KT><<<B * T, 256, 0, s>>>(m->pqkv, (KT*)kc, (KT*)vc, T, m->Hl, m->hd, m->C, m->Dl);
+    dim3 grid(rg_cdiv(T, 8), m->Hl, B);
     const float scale = 1.f / sqrtf((float)m->hd);
     const int causal = m->cfg.causal ? 1 : 0;
     if (m->hd == 32)
-        rg_attn_rows_kernel<KT, 32><<<grid, 256, 0, s>>>(m->pqkv, kc, vc, m->pattn, T, m->H, m->C, m->D, scale, causal);
+        rg_attn_rows_kernel<KT, 32><<<grid, 256, 0, s>>>(m->pqkv, kc, vc, m->pattn, T, m->Hl, m->C, m->Dl, scale, causal);
     else if (m->hd == 64)
-        rg_attn_rows_kernel<KT, 64><<<grid, 256, 0, s>>>(m->pqkv, kc, vc, m->pattn, T, m->H, m->C, m->D, scale, causal);
+        rg_attn_rows_kernel<KT, 64><<<grid, 256, 0, s>>>(m->pqkv, kc, vc, m->pattn, T, m->Hl, m->C, m->Dl, scale, causal);
     else
-        rg_attn_rows_kernel<KT, 128><<<grid, 256, 0, s>>>(m->pqkv, kc, vc, m->pattn, T, m->H, m->C, m->D, scale, causal);
+        rg_attn_rows_kernel<KT, 128><<<grid, 256, 0, s>>>(m->pqkv, kc, vc, m->pattn, T, m->Hl, m->C, m->Dl, scale, causal);
     m->ctx->launches += 2;
     RG_CUDA(cudaGetLastError());
+    return RG_OK;
+}
+
+// x += A . W + b for a row-split projection: every rank holds a K-slice, the partial products are summed
+// over the ranks (NCCL all-reduce over NVLink), bias and residual are added once.
+static rg_status gemm_rowsplit_residual(rg_gpt* m, const float* A, int M, const rg_linear& lin, float* x) {
+    if (m->tp_size == 1) return gemm(m, A, M, lin, x, x, -1);
+    RG_TRY(gemm(m, A, M, lin, m->ptp, nullptr, -1, false));
+    RG_TRY(tp_allreduce(m, m->ptp, (size_t)M * lin.N));
+    rg_add_bias_res_kernel<<<rg_cdiv((long long)M * lin.N, 256), 256, 0, m->ctx->stream>>>(x, m->ptp, lin.b, (size_t)M, lin.N);
+    RG_LAUNCHED(m->ctx);
+    return RG_OK;
+}
+
+// logits of `rows` rows: local vocabulary slice, then (tensor parallel) all-gather and re-interleave
+static rg_status head_logits(rg_gpt* m, const float* A, int rows, float* logits) {
+    if (m->tp_size == 1) return gemm(m, A, rows, m->head, logits, nullptr, -1);
+    const size_t per = (size_t)rows * m->Vpad;
+    if (per * (m->tp_size + 1) > m->pgatherCap) {
+        RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+        dfree(m, m->pgather);
+        m->pgather = nullptr, m->pgatherCap = 0;
+        RG_TRY(dalloc(m, (void**)&m->pgather, per * (m->tp_size + 1) * 4));
+        m->pgatherCap = per * (m->tp_size + 1);
+    }
+    float* local = m->pgather + per * m->tp_size;
+    RG_CUDA(cudaMemsetAsync(local, 0, per * 4, m->ctx->stream));
+    RG_TRY(gemm(m, A, rows, m->head, local, nullptr, -1, true, m->Vpad));
+    RG_TRY(tp_allgather(m, local, m->pgather, per));
+    rg_ungather_logits_kernel<<<rg_cdiv((long long)rows * m->V, 256), 256, 0, m->ctx->stream>>>(m->pgather, logits, (size_t)rows,
+                                                                                                m->V, m->Vpad);
+    RG_LAUNCHED(m->ctx);
     return RG_OK;
 }
 
@@ -333,6 +486,7 @@ static rg_status attn_rows(rg_gpt* m, int l, int B, int T) {
 // m->picks / tokens[b][T].
 static rg_status run_rows(rg_gpt* m, int B, int T, float* full) {
     const int M = B * T, D = m->D;
+    RG_TRY(tp_ready(m));
     RG_TRY(ensure_rows(m, (size_t)M));
     cudaStream_t s = m->ctx->stream;
     if (m->bf16)
@@ -350,21 +504,21 @@ static rg_status run_rows(rg_gpt* m, int B, int T, float* full) {
         RG_TRY(gemm(m, m->pln, M, y.qkv, m->pqkv, nullptr, -1));
         if (m->bf16) RG_TRY(attn_rows<__nv_bfloat16>(m, l, B, T));
         else RG_TRY(attn_rows<float>(m, l, B, T));
-        RG_TRY(gemm(m, m->pattn, M, y.o, m->px, m->px, -1));
+        RG_TRY(gemm_rowsplit_residual(m, m->pattn, M, y.o, m->px));
         rg_ln_rows_kernel<<<rg_cdiv(M, 8), 256, 0, s>>>(m->px, D, y.ln2g, y.ln2b, m->pln, (size_t)M, D, 1e-5f);
         RG_LAUNCHED(m->ctx);
         RG_TRY(gemm(m, m->pln, M, y.fc1, m->ph, nullptr, act));
-        RG_TRY(gemm(m, m->ph, M, y.fc2, m->px, m->px, -1));
+        RG_TRY(gemm_rowsplit_residual(m, m->ph, M, y.fc2, m->px));
     }
     if (full) {
         rg_ln_rows_kernel<<<rg_cdiv(M, 8), 256, 0, s>>>(m->px, D, m->lnfg, m->lnfb, m->pln, (size_t)M, D, 1e-5f);
         RG_LAUNCHED(m->ctx);
-        RG_TRY(gemm(m, m->pln, M, m->head, full, nullptr, -1));
+        RG_TRY(head_logits(m, m->pln, M, full));
     } else {
         rg_ln_rows_kernel<<<rg_cdiv(B, 8), 256, 0, s>>>(m->px + (size_t)(T - 1) * D, (long long)T * D, m->lnfg, m->lnfb,
                                                         m->plast, (size_t)B, D, 1e-5f);
         RG_LAUNCHED(m->ctx);
-        RG_TRY(gemm(m, m->plast, B, m->head, m->logits, nullptr, -1));
+        RG_TRY(head_logits(m, m->plast, B, m->logits));
         rg_argmax_rows_kernel<<<B, 1024, 0, s>>>(m->logits, m->V, m->picks, m->tokens, m->C, T);
         RG_LAUNCHED(m->ctx);
     }
@@ -496,13 +650,28 @@ static void launch_attn_step(rg_gpt* m, int l, int B) {
     a.qkv_parts = y.qkv.parts, a.nparts = y.qkv.ksplit, a.qkv_bias = y.qkv.b;
     a.kcache = m->kc + (size_t)l * m->kv_layer_bytes, a.vcache = m->vc + (size_t)l * m->kv_layer_bytes;
     a.ap = m->ap, a.pos = m->d_pos;
-    a.B = B, a.H = m->H, a.C = m->C, a.D = m->D, a.NS = m->NS;
+    a.B = B, a.H = m->Hl, a.C = m->C, a.D = m->Dl, a.NS = m->NS;
     a.scale = 1.f / sqrtf((float)m->hd);
-    dim3 grid(m->NS, m->H, B);
+    dim3 grid(m->NS, m->Hl, B);
     cudaStream_t s = m->ctx->stream;
     if (m->hd == 32) rg_attn_step_kernel<KT, 32><<<grid, 128, 0, s>>>(a);
     else if (m->hd == 64) rg_attn_step_kernel<KT, 64><<<grid, 128, 0, s>>>(a);
     else rg_attn_step_kernel<KT, 128><<<grid, 128, 0, s>>>(a);
+}
+
+// Enqueue the kernels of one token step for B sequences; returns how many.
+// Tensor parallel: the k-split partials of a row-split projection are summed locally, then over the ranks;
+// returns the "producer" the next stage reads (one part: the reduced vector).
+static rg_linear tp_reduce(rg_gpt* m, const rg_linear& lin, int B, int* n) {
+    rg_linear r = lin;
+    if (m->tp_size == 1) return r;
+    const size_t cnt = (size_t)B * lin.N;
+    rg_reduce_parts_kernel<<<rg_cdiv((long long)cnt, 256), 256, 0, m->ctx->stream>>>(lin.parts, lin.ksplit, cnt, nullptr, 1,
+                                                                                   m->tp_vec);
+    g_nccl.AllReduce(m->tp_vec, m->tp_vec, cnt, ncclFloat32, ncclSum, (ncclComm_t)m->nccl_comm, m->ctx->stream);
+    *n += 2;
+    r.parts = m->tp_vec, r.ksplit = 1;
+    return r;
 }
 
 // Enqueue the kernels of one token step for B sequences; returns how many.
@@ -518,37 +687,55 @@ static int enqueue_step(rg_gpt* m, int B) {
                                                       m->ldt, m->xa, m->d_pos_next, m->d_pos);
     n++;
     const int act_post = m->cfg.activation == RG_ACT_RELU ? RG_POST_RELU : RG_POST_GELU;
+    rg_linear prev_fc2;  // producer of the block input (reduced over the ranks when tensor parallel)
+    const float* prev_b2 = nullptr;
+    bool have_prev = false;
     for (int l = 0; l < m->L; l++) {
         rg_layer& y = m->layers[l];
-        const rg_layer* prev = l ? &m->layers[l - 1] : nullptr;
-        // x = x + b2 + fc2 partials of the previous block; LN1; QKV
-        rg_vec_in in = vec_reduce(m->xa, prev ? prev->fc2.b : nullptr, prev ? &prev->fc2 : nullptr, RG_POST_LN);
+        // x = x + b2 + fc2 partials of the previous block; LN1; QKV (this rank's heads)
+        rg_vec_in in = vec_reduce(m->xa, prev_b2, have_prev ? &prev_fc2 : nullptr, RG_POST_LN);
         in.gamma = y.ln1g, in.beta = y.ln1b, in.store = m->xb;
         launch_gemv(m, y.qkv, in, B);
         if (m->bf16) launch_attn_step<__nv_bfloat16>(m, l, B);
         else launch_attn_step<float>(m, l, B);
-        // merged heads -> output projection
+        // merged heads -> output projection (row-split over the ranks' heads)
         rg_vec_in ia;
         memset(&ia, 0, sizeof(ia));
-        ia.kind = RG_IN_ATTN, ia.ap = m->ap, ia.H = m->H, ia.hd = m->hd, ia.NS = m->NS, ia.post = RG_POST_NONE;
+        ia.kind = RG_IN_ATTN, ia.ap = m->ap, ia.H = m->Hl, ia.hd = m->hd, ia.NS = m->NS, ia.post = RG_POST_NONE;
         launch_gemv(m, y.o, ia, B);
-        // x = x + bo + partials; LN2; FC1
-        rg_vec_in i1 = vec_reduce(m->xb, y.o.b, &y.o, RG_POST_LN);
+        const rg_linear o_red = tp_reduce(m, y.o, B, &n);
+        // x = x + bo + partials; LN2; FC1 (this rank's hidden columns)
+        rg_vec_in i1 = vec_reduce(m->xb, y.o.b, &o_red, RG_POST_LN);
         i1.gamma = y.ln2g, i1.beta = y.ln2b, i1.store = m->xa;
         launch_gemv(m, y.fc1, i1, B);
-        // act(b1 + partials); FC2
+        // act(b1 + partials); FC2 (row-split)
         rg_vec_in i2 = vec_reduce(nullptr, y.fc1.b, &y.fc1, act_post);
         launch_gemv(m, y.fc2, i2, B);
+        prev_fc2 = tp_reduce(m, y.fc2, B, &n);
+        prev_b2 = y.fc2.b;
+        have_prev = true;
         n += 5;
     }
-    const rg_layer& last = m->layers[m->L - 1];
-    rg_vec_in ih = vec_reduce(m->xa, last.fc2.b, &last.fc2, RG_POST_LN);
+    rg_vec_in ih = vec_reduce(m->xa, prev_b2, &prev_fc2, RG_POST_LN);
     ih.gamma = m->lnfg, ih.beta = m->lnfb, ih.store = nullptr;
     launch_gemv(m, m->head, ih, B);
     rg_pick_args pa;
     pa.parts = m->head.parts, pa.nparts = m->head.ksplit, pa.bias = m->head.b, pa.logits = m->logits;
     pa.tokens = m->tokens, pa.picks = m->picks, pa.pos = m->d_pos, pa.pos_next = m->d_pos_next;
     pa.B = B, pa.V = m->V, pa.C = m->C;
+    if (m->tp_size > 1) {
+        // vocabulary slices: local logits (+bias) -> all-gather -> full rows in m->logits -> pick
+        const size_t per = (size_t)B * m->Vpad;
+        cudaMemsetAsync(m->tp_local, 0, per * 4, s);
+        rg_reduce_parts_kernel<<<rg_cdiv((long long)B * m->Vl, 256), 256, 0, s>>>(m->head.parts, m->head.ksplit,
+                                                                                 (size_t)B * m->Vl, m->head.b, m->Vl, m->tp_local,
+                                                                                 m->Vpad);
+        g_nccl.AllGather(m->tp_local, m->tp_gather, per, ncclFloat32, (ncclComm_t)m->nccl_comm, s);
+        rg_ungather_logits_kernel<<<rg_cdiv((long long)B * m->V, 256), 256, 0, s>>>(m->tp_gather, m->logits, (size_t)B, m->V,
+                                                                                   m->Vpad);
+        pa.parts = m->logits, pa.nparts = 1, pa.bias = nullptr;
+        n += 4;
+    }
     rg_pick_kernel<<<B, 1024, 0, s>>>(pa);
     n += 2;
     return n;
@@ -559,6 +746,7 @@ static rg_status step_ready(rg_gpt* m, size_t steps) {
         return rg_fail(RG_ERR_UNSUPPORTED,
                        "the KV-cache token step needs causal attention; this model uses the reference's unmasked attention");
     if (m->curB == 0) return rg_fail(RG_ERR_INVALID_INPUT, "no context: call rg_gpt_prefill first");
+    RG_TRY(tp_ready(m));
     if (m->pos + steps > (size_t)m->C)
         return rg_fail(RG_ERR_CONTEXT_FULL, "context full: position %zu + %zu steps exceeds block_size %d", m->pos, steps, m->C);
     return RG_OK;
@@ -723,6 +911,29 @@ extern "C" double rg_gpt_decode_step_bytes(const rg_gpt* m, size_t B, double mea
     const double w = L * (12.0 * D * D + 13.0 * D) + D * V + V + 4.0 * D;
     const double kv = m->bf16 ? 2.0 : 4.0;
     return (double)m->wsize * w + (double)B * kv * 2.0 * L * D * mean_ctx;
+}
+
+extern "C" rg_status rg_gpt_tp_unique_id(uint8_t id_out[128]) {
+    if (!id_out) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    RG_TRY(load_nccl());
+    ncclUniqueId id;
+    RG_NCCL(g_nccl.GetUniqueId(&id));
+    memcpy(id_out, id.internal, 128);
+    return RG_OK;
+}
+
+extern "C" rg_status rg_gpt_tp_init(rg_gpt* m, const uint8_t id_in[128]) {
+    if (!m || !id_in) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+    if (m->tp_size <= 1) return rg_fail(RG_ERR_INVALID_INPUT, "the model was created with tp_size <= 1");
+    if (m->nccl_comm) return rg_fail(RG_ERR_INVALID_INPUT, "the communicator exists already");
+    RG_TRY(load_nccl());
+    rg_ctx_guard g(m->ctx);
+    ncclUniqueId id;
+    memcpy(id.internal, id_in, 128);
+    ncclComm_t comm = nullptr;
+    RG_NCCL(g_nccl.CommInitRank(&comm, m->tp_size, id, m->tp_rank));
+    m->nccl_comm = comm;
+    return RG_OK;
 }
 
 extern "C" rg_status rg_gpt_trace_enable(rg_gpt* m, int on) {

@@ -22,6 +22,14 @@ struct rg_gpt {
     rg_ctx* ctx = nullptr;
     rg_gpt_config cfg;
     int V = 0, D = 0, L = 0, H = 0, hd = 0, C = 0, F = 0, Bmax = 1;
+    // tensor-parallel shard of this rank (the full sizes when tp_size == 1): heads [h0, h0+Hl), hidden columns
+    // [f0, f0+Fl), vocabulary [v0, v0+Vl); Dl = Hl * hd; Vpad = vocabulary slice size of every rank but the last
+    int tp_rank = 0, tp_size = 1;
+    int Hl = 0, h0 = 0, Dl = 0, Fl = 0, f0 = 0, Vl = 0, v0 = 0, Vpad = 0;
+    void* nccl_comm = nullptr;
+    float *tp_vec = nullptr, *tp_gather = nullptr, *tp_local = nullptr;  // token-step collectives
+    float *ptp = nullptr, *pgather = nullptr;                           // prompt-pass collectives
+    size_t pgatherCap = 0;
     bool bf16 = false, loaded = false;
     size_t wsize = 4;
     long long ldt = 0;  // leading dimension of the two embedding tables

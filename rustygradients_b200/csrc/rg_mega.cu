@@ -25,6 +25,7 @@
 //    global flag, drains its own copies and returns; the host reports RG_ERR_TIMEOUT.
 #include "rg_gpt.h"
 
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -79,6 +80,7 @@ struct mg_params {
     int pos0, n_steps;
     uint32_t epoch0;
     int nslot, max_ops, max_cd, res_cap, n_pick_ctas;
+    int poll_sleep;
     int S;  // CTAs that share one (sequence, head) in the attention stage, each a slice of the context
     int res_q0, res_nq;  // residual slice = column groups [res_q0, res_q0 + res_nq) of the N=D stages (per CTA: via ops)
     float scale;
@@ -210,6 +212,7 @@ __device__ __forceinline__ void mg_mbar_arrive(uint64_t* bar) {
 // Per-thread control state.  `dead` becomes CTA-wide at the next op boundary.
 struct mg_ctl {
     int* abort_flag;
+    unsigned poll_sleep;  // ns to pause between two polls of words that were not valid yet (0 = none)
     bool dead;
 };
 __device__ __forceinline__ void mg_give_up(mg_ctl& c) {
@@ -361,7 +364,7 @@ __device__ __noinline__ void mg_fetch(const mg_word* src, int n, uint32_t tag, f
                     mg_give_up(ctl);
                     break;
                 }
-                __nanosleep(64);
+                if (ctl.poll_sleep) __nanosleep(ctl.poll_sleep);
             }
         }
         if (ctl.dead) break;
@@ -563,6 +566,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
     // =================== consumer warps ===================
     mg_ctl ctl;
     ctl.abort_flag = p.abort_flag;
+    ctl.poll_sleep = (unsigned)p.poll_sleep;
     ctl.dead = false;
     mg_cons ring;
     ring.slots = slots, ring.full = full, ring.empty = empty, ring.nslot = p.nslot, ring.slot = 0, ring.parity = 0;
@@ -1255,7 +1259,7 @@ static rg_status mg_prepare(rg_gpt* m, int B) {
 }
 
 bool rg_mega_supports(const rg_gpt* m, int B) {
-    return m->mega != nullptr && m->use_mega && m->cfg.causal && mg_variant(B) >= 0 && m->hd <= 128;
+    return m->mega != nullptr && m->use_mega && m->cfg.causal && m->tp_size == 1 && mg_variant(B) >= 0 && m->hd <= 128;
 }
 
 rg_status rg_mega_create(rg_gpt* m) {
@@ -1305,6 +1309,10 @@ rg_status rg_mega_run(rg_gpt* m, int B, size_t pos0, size_t n_steps) {
     prm.act = m->cfg.activation;
     prm.pos0 = (int)pos0, prm.n_steps = (int)n_steps, prm.epoch0 = m->epoch;
     prm.S = g->S;
+    {
+        const char* ps = getenv("RG_B200_POLL_SLEEP_NS");
+        prm.poll_sleep = ps ? atoi(ps) : 0;
+    }
     prm.nslot = g->nslot, prm.max_ops = g->max_ops, prm.res_cap = g->res_cap, prm.n_pick_ctas = g->n_pick_ctas;
     prm.scale = 1.f / sqrtf((float)m->hd);
     cudaError_t e;

@@ -25,6 +25,8 @@ class GptConfig:
     activation: str = "gelu_tanh"   # or "relu" (the reference's FeedForward)
     weight_dtype: str = "f32"       # or "bf16"
     max_batch: int = 1
+    tp_rank: int = 0
+    tp_size: int = 1
 
 
 class GPTModel:
@@ -39,10 +41,21 @@ class GPTModel:
                             config.embedding_dim, 1 if config.causal else 0,
                             {"relu": _lib.RG_ACT_RELU, "gelu_tanh": _lib.RG_ACT_GELU_TANH}[config.activation],
                             {"f32": _lib.RG_DTYPE_F32, "bf16": _lib.RG_DTYPE_BF16}[config.weight_dtype],
-                            config.max_batch)
+                            config.max_batch, config.tp_rank, config.tp_size)
         h = C.c_void_p()
         check(self._lib.rg_gpt_create(backend._ctx, C.byref(c), C.byref(h)))
         self._h = h
+
+    # -- tensor parallelism: one NCCL communicator over the ranks that hold the model's shards
+    @staticmethod
+    def tp_unique_id() -> bytes:
+        buf = (C.c_uint8 * 128)()
+        check(_lib.load().rg_gpt_tp_unique_id(buf))
+        return bytes(buf)
+
+    def tp_init(self, unique_id: bytes) -> None:
+        buf = (C.c_uint8 * 128)(*unique_id)
+        check(self._lib.rg_gpt_tp_init(self._h, buf))
 
     def close(self) -> None:
         if self._h:
