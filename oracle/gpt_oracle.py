@@ -321,6 +321,24 @@ def sample_topk(logits: np.ndarray, temperature: float, top_k: int, u: float) ->
     return 0
 
 
+_M64 = (1 << 64) - 1
+
+
+def _splitmix64(x: int) -> int:
+    x = (x + 0x9E3779B97F4A7C15) & _M64
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & _M64
+    return x ^ (x >> 31)
+
+
+def uniform_draw(seed: int, seq: int, step: int) -> float:
+    """The engine's stand-in for the reference's unseeded `rng.gen::<f32>()`
+    (src/wasm_api.rs:145): a counter-based draw in [0,1) with 24 random bits, keyed
+    by (seed, sequence, step)."""
+    h = _splitmix64((_splitmix64((seed ^ ((0xD1B54A32D192ED03 * (seq + 1)) & _M64)) & _M64) + step) & _M64)
+    return float(np.float32(h >> 40) * np.float32(1.0 / 16777216.0))
+
+
 def greedy_pick(logits_row: np.ndarray) -> int:
     """top_k = 1 in src/wasm_api.rs:123-156: only the maximum survives with
     probability 1.  Ties: lowest index (the reference's unstable sort leaves

@@ -6,6 +6,7 @@
 #include "rg_gemm.cuh"
 #include "rg_decode_kernels.cuh"
 #include "rg_prefill_kernels.cuh"
+#include "rg_sample.cuh"
 
 #include <math.h>
 #include <stdlib.h>
@@ -851,14 +852,26 @@ extern "C" rg_status rg_gpt_reset(rg_gpt* m) {
 // ---------------------------------------------------------------------------
 // generate
 // ---------------------------------------------------------------------------
+// Draw the id at `slot` of every sequence from the finished logits rows (m->logits).
+static rg_status sample_rows(rg_gpt* m, int B, size_t slot, float temperature, size_t top_k, uint64_t seed, unsigned step) {
+    rg_sample_args a;
+    a.logits = m->logits, a.tokens = m->tokens, a.picks = m->picks;
+    a.V = m->V, a.C = m->C, a.slot = (int)slot;
+    a.top_k = top_k >= (size_t)m->V ? 0 : (int)top_k;
+    a.inv_temperature = 1.f / temperature;
+    a.seed = seed, a.step = step;
+    rg_sample_kernel<<<B, 1024, 0, m->ctx->stream>>>(a);
+    RG_LAUNCHED(m->ctx);
+    RG_CUDA(cudaGetLastError());
+    return RG_OK;
+}
+
 extern "C" rg_status rg_gpt_generate(rg_gpt* m, const uint32_t* prompt, size_t B, size_t P, size_t max_new,
                                      float temperature, size_t top_k, uint64_t seed, uint32_t* out) {
-    (void)temperature;
-    (void)seed;
     if (!m || !prompt || (!out && max_new)) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
     RG_TRY(check_ready(m, B));
-    if (top_k != 1)
-        return rg_fail(RG_ERR_UNSUPPORTED, "only greedy decoding (top_k = 1) is implemented; got top_k = %zu", top_k);
+    const bool greedy = top_k == 1;
+    if (!greedy && !(temperature > 0.f)) return rg_fail(RG_ERR_INVALID_INPUT, "temperature must be positive, got %g", (double)temperature);
     if (P == 0) return rg_fail(RG_ERR_INVALID_INPUT, "empty prompt");
     if (max_new == 0) return RG_OK;
     rg_ctx_guard g(m->ctx);
@@ -868,7 +881,16 @@ extern "C" rg_status rg_gpt_generate(rg_gpt* m, const uint32_t* prompt, size_t B
                            "prompt %zu + %zu new ids needs %zu cache rows, block_size is %d (the KV cache cannot slide)", P,
                            max_new, P + max_new - 1, m->C);
         RG_TRY(prefill_locked(m, prompt, B, P, nullptr, nullptr));
-        if (max_new > 1) RG_TRY(run_steps(m, max_new - 1));
+        if (greedy) {
+            if (max_new > 1) RG_TRY(run_steps(m, max_new - 1));
+        } else {
+            // one step at a time: the draw replaces the greedy pick the step left at the next position
+            RG_TRY(sample_rows(m, (int)B, P, temperature, top_k, seed, 0));
+            for (size_t i = 1; i < max_new; i++) {
+                RG_TRY(run_steps(m, 1));
+                RG_TRY(sample_rows(m, (int)B, P + i, temperature, top_k, seed, (unsigned)i));
+            }
+        }
         if (P + max_new <= (size_t)m->C) {
             RG_CUDA(cudaMemcpy2DAsync(out, max_new * 4, m->tokens + P, (size_t)m->C * 4, max_new * 4, B,
                                       cudaMemcpyDeviceToHost, m->ctx->stream));
@@ -894,6 +916,7 @@ extern "C" rg_status rg_gpt_generate(rg_gpt* m, const uint32_t* prompt, size_t B
         for (size_t b = 0; b < B; b++) memcpy(&window[b * T], &ids[b][start], T * 4);
         RG_TRY(upload_ids(m, window.data(), B, T));
         RG_TRY(run_rows(m, (int)B, (int)T, nullptr));
+        if (!greedy) RG_TRY(sample_rows(m, (int)B, (size_t)m->C, temperature, top_k, seed, (unsigned)i));
         RG_CUDA(cudaMemcpyAsync(picks.data(), m->picks, B * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
         RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
         for (size_t b = 0; b < B; b++) {

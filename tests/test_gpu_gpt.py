@@ -211,3 +211,43 @@ def test_model_errors(backend):
     # still usable afterwards
     lg = m.forward(np.array([[1, 2, 3]], np.float32))
     assert np.abs(lg - O.forward(params, cfg, np.array([[1, 2, 3]]), causal=True, act="gelu_tanh")).max() <= F32_TOL
+
+
+# ---- stochastic sampling: top-k filter, temperature, inverse-CDF draw (src/wasm_api.rs:120-156)
+def test_topk_temperature_sampling(backend):
+    cfg = O.GptConfig(40, 301, 2, 3, 96)
+    params = O.make_params(cfg, 5, stress=True)
+    B, P, G = 3, 9, 14
+    prompt = O.make_prompt(cfg, 8, B, P)
+    m = model_for(backend, cfg, params, max_batch=4)
+    for temperature, top_k, seed in ((0.9, 7, 5), (1.3, 0, 11), (0.7, 301, 3), (2.0, 40, 99)):
+        out = m.generate(prompt, G, temperature=temperature, top_k=top_k, seed=seed)
+        assert np.array_equal(out, m.generate(prompt, G, temperature=temperature, top_k=top_k, seed=seed))   # reproducible
+        ids = np.concatenate([prompt, out], 1)
+        logits, _ = teacher_forced(m, ids, P)            # the rows each draw was made from
+        agree = 0
+        for b in range(B):
+            for i in range(G):
+                lg = logits[b, i].astype(np.float64)
+                u = O.uniform_draw(seed, b, i)
+                keep = np.ones(cfg.vocab_size, bool)
+                if 0 < top_k < cfg.vocab_size:
+                    keep[:] = False
+                    keep[np.argsort(-lg, kind="stable")[:top_k]] = True
+                pr = np.where(keep, np.exp((lg - lg.max()) / temperature), 0.0)
+                cdf = np.cumsum(pr) / pr.sum()
+                tok = int(out[b, i])
+                assert keep[tok]
+                lo = cdf[tok - 1] if tok else 0.0
+                assert lo - 1e-5 <= u <= cdf[tok] + 1e-5          # the inverse-CDF walk stopped at the right id
+                agree += O.sample_topk(logits[b, i], temperature, top_k, u) == tok
+        assert agree >= B * G - 2                                   # the oracle's f32 walk agrees away from boundaries
+    assert not np.array_equal(m.generate(prompt, G, temperature=1.0, top_k=50, seed=1),
+                              m.generate(prompt, G, temperature=1.0, top_k=50, seed=2))
+    assert np.array_equal(m.generate(prompt, G, temperature=5.0, top_k=1, seed=7), m.generate(prompt, G))  # top_k 1 is greedy
+    with pytest.raises(rg.InvalidInput):
+        m.generate(prompt, G, temperature=0.0, top_k=5)
+    # the reference's loop (no mask, full re-forward) with sampling
+    mr = model_for(backend, cfg, params, causal=False, act="relu", max_batch=4)
+    a = mr.generate(prompt, 6, temperature=0.8, top_k=10, seed=4)
+    assert a.shape == (B, 6) and np.array_equal(a, mr.generate(prompt, 6, temperature=0.8, top_k=10, seed=4))
