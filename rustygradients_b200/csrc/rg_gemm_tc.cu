@@ -1,0 +1,250 @@
+// Tensor-core GEMM of the prompt pass in bf16-weight mode (sm_100a only):
+//
+//   C[M,N] (f32) = epi( A[M,K] (bf16, row-major) . Wt[N,K]^T (bf16, K contiguous) )
+//   epi(v) = act(v + bias[n]) + res[m][n]
+//
+// This is Linear::forward (src/nn/linear.rs:50-56) on all rows of a prompt at once,
+// the one place on the path that is a dense contraction.  5th-generation tensor cores:
+//  * operands are staged by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a 4-stage
+//    shared-memory ring, 128x64 bf16 tiles of A and of Wt per stage;
+//  * one elected thread issues tcgen05.mma (M=128, N=128, K=16, kind::f16, fp32
+//    accumulate) with shared-memory matrix descriptors; the accumulator lives in TMEM
+//    (128 lanes x 128 columns);
+//  * tcgen05.commit signals "stage consumed" and "accumulator complete" on mbarriers;
+//  * four epilogue warps read the accumulator back with tcgen05.ld (32 lanes x 32
+//    columns at a time) and apply bias / activation / residual on the way to HBM.
+// No cluster multicast anywhere.  Every wait is bounded: on expiry the CTA raises an
+// error word, still frees its TMEM and returns.
+#include "rg_internal.cuh"
+
+#include <cuda.h>
+
+#define TC_BM 128
+#define TC_BN 128
+#define TC_BK 64
+#define TC_STAGES 4
+#define TC_THREADS 192
+#define TC_SPIN_LIMIT (1u << 22)
+#define TC_STAGE_BYTES ((TC_BM + TC_BN) * TC_BK * 2)
+#define TC_SMEM_BYTES (TC_STAGES * TC_STAGE_BYTES + 1024 + 256)
+
+struct tc_epi {
+    float* C;
+    long long ldc;
+    const float* bias;
+    const float* res;
+    long long ldres;
+    int act;
+    int M, N, K;
+    int* err;
+};
+
+__device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, int* err) {
+    uint32_t ok = 0, spins = 0;
+    while (true) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(tc_smem(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (++spins > TC_SPIN_LIMIT) {
+            atomicExch(err, 1);
+            return false;
+        }
+    }
+}
+
+// Shared-memory matrix descriptor: K-major tile whose rows are 128 bytes (64 bf16), 128-byte swizzle,
+// 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);  // start address
+    d |= (uint64_t)0 << 16;                       // leading byte offset: unused for swizzled K-major
+    d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                       // descriptor version
+    d |= (uint64_t)2 << 61;                       // 128-byte swizzle
+    return d;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const tc_epi e) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    // 1024-byte aligned tiles (the swizzle pattern is a function of the address)
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + TC_STAGES * TC_STAGE_BYTES);
+    uint64_t* empty = full + TC_STAGES;
+    uint64_t* acc_full = empty + TC_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
+    const int nkb = e.K / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&full[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&empty[s])) : "memory");
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(acc_full)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // the MMA warp owns the tensor memory: 128 columns of fp32 accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;" ::"r"(tc_smem(tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ===== TMA producer =====
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % TC_STAGES;
+                const uint32_t par = (kb / TC_STAGES) & 1;
+                if (!tc_wait(&empty[s], par ^ 1u, e.err)) break;
+                unsigned char* a_dst = tiles + s * TC_STAGE_BYTES;
+                unsigned char* b_dst = a_dst + TC_BM * TC_BK * 2;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full[s])),
+                             "r"((uint32_t)TC_STAGE_BYTES)
+                             : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                        tc_smem(a_dst)),
+                    "l"(&tmA), "r"(kb * TC_BK), "r"(m0), "r"(tc_smem(&full[s]))
+                    : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                        tc_smem(b_dst)),
+                    "l"(&tmB), "r"(kb * TC_BK), "r"(n0), "r"(tc_smem(&full[s]))
+                    : "memory");
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer =====
+        if (lane == 0) {
+            // instruction descriptor: D = f32, A = B = bf16, both K-major, N = 128, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; kb++) {
+                const int s = kb % TC_STAGES;
+                const uint32_t par = (kb / TC_STAGES) & 1;
+                ok = tc_wait(&full[s], par, e.err);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = tc_smem(tiles + s * TC_STAGE_BYTES);
+                const uint32_t b_addr = a_addr + TC_BM * TC_BK * 2;
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; k++) {
+                    const uint64_t da = tc_desc(a_addr + k * 32);  // 16 bf16 = 32 bytes further along K inside the swizzle span
+                    const uint64_t db = tc_desc(b_addr + k * 32);
+                    const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_base),
+                        "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+                        : "memory");
+                }
+                // the stage is free again once these MMAs have read it
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&empty[s]))
+                             : "memory");
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(acc_full))
+                         : "memory");
+        }
+    } else {
+        // ===== epilogue warps 2..5: TMEM lane quarter = warp % 4 =====
+        const int q = warp & 3;
+        const bool ok = tc_wait(acc_full, 0, e.err);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int m = m0 + q * 32 + lane;
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < TC_BN / 32; c++) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                      "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                      "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (m < e.M) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int n = n0 + c * 32 + j;
+                        if (n < e.N) {
+                            float v = __uint_as_float(r[j]);
+                            if (e.bias) v += e.bias[n];
+                            if (e.act >= 0) v = rg_apply_act(v, e.act);
+                            if (e.res) v += e.res[(long long)m * e.ldres + n];
+                            e.C[(long long)m * e.ldc + n] = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" ::"r"(tmem_base) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*tc_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static tc_encode_fn g_encode = nullptr;
+
+static rg_status tc_make_map(CUtensorMap* map, const void* base, int rows, int K) {
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {TC_BK, TC_BM};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return rg_fail(RG_ERR_BACKEND, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return RG_OK;
+}
+
+// Returns RG_ERR_UNSUPPORTED (without touching C) when the shape is outside the kernel's limits.
+rg_status rg_gemm_bf16_tc(rg_ctx* ctx, const void* A16, int M, int K, const void* Wt16, int N, float* C, long long ldc,
+                          const float* bias, const float* res, long long ldres, int act) {
+    if (K % TC_BK != 0 || K < TC_BK || M <= 0 || N <= 0) return RG_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(A16) & 15) || (reinterpret_cast<uintptr_t>(Wt16) & 15)) return RG_ERR_UNSUPPORTED;
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t er = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (er != cudaSuccess || !fn || qres != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            return RG_ERR_UNSUPPORTED;
+        }
+        g_encode = reinterpret_cast<tc_encode_fn>(fn);
+        cudaError_t ea = cudaFuncSetAttribute(rg_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+        if (ea != cudaSuccess) return rg_fail(RG_ERR_BACKEND, "rg_gemm_tc_kernel: %s", cudaGetErrorString(ea));
+    }
+    CUtensorMap tmA, tmB;
+    RG_TRY(tc_make_map(&tmA, A16, M, K));
+    RG_TRY(tc_make_map(&tmB, Wt16, N, K));
+    tc_epi e;
+    e.C = C, e.ldc = ldc, e.bias = bias, e.res = res, e.ldres = ldres, e.act = act, e.M = M, e.N = N, e.K = K;
+    e.err = ctx->d_flag + 1;
+    dim3 grid(rg_cdiv(N, TC_BN), rg_cdiv(M, TC_BM));
+    rg_gemm_tc_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(tmA, tmB, e);
+    RG_CUDA(cudaGetLastError());
+    RG_LAUNCHED(ctx);
+    return RG_OK;
+}

@@ -82,6 +82,33 @@ static __global__ void rg_ungather_logits_kernel(const float* __restrict__ g, fl
     logits[i] = g[((size_t)rank * rows + r) * Vpad + (v - rank * Vpad)];
 }
 
+// Wt[n][k] = W[k][n] (bf16), 32x32 tiles through shared memory
+static __global__ void rg_transpose_bf16_kernel(const __nv_bfloat16* __restrict__ W, long long ldw, int K, int N,
+                                                __nv_bfloat16* __restrict__ Wt) {
+    __shared__ __nv_bfloat16 t[32][33];
+    const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int k = k0 + i, n = n0 + threadIdx.x;
+        t[i][threadIdx.x] = (k < K && n < N) ? W[(size_t)k * ldw + n] : __float2bfloat16_rn(0.f);
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int n = n0 + i, k = k0 + threadIdx.x;
+        if (n < N && k < K) Wt[(size_t)n * K + k] = t[threadIdx.x][i];
+    }
+}
+static __global__ void rg_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, size_t n) {
+    size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 3 < n) {
+        const float4 v = *reinterpret_cast<const float4*>(x + i);
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<__nv_bfloat162*>(y + i) = a;
+        *reinterpret_cast<__nv_bfloat162*>(y + i + 2) = b;
+    } else {
+        for (; i < n; i++) y[i] = __float2bfloat16_rn(x[i]);
+    }
+}
+
 static __global__ void rg_set_int2_kernel(int* a, int* b, int v) {
     *a = v;
     if (b) *b = v;
@@ -124,6 +151,7 @@ static rg_status alloc_linear(rg_gpt* m, rg_linear& lin, int K, int N) {
     RG_TRY(dalloc(m, &lin.W, (size_t)K * lin.ldw * m->wsize));
     RG_CUDA(cudaMemset(lin.W, 0, (size_t)K * lin.ldw * m->wsize));
     RG_TRY(dalloc(m, (void**)&lin.b, (size_t)N * 4));
+    if (m->bf16 && m->use_tc && K % 64 == 0) RG_TRY(dalloc(m, &lin.Wt, (size_t)N * K * 2));
     plan_split(m, lin);
     RG_TRY(dalloc(m, (void**)&lin.parts, (size_t)lin.ksplit * m->Bmax * N * 4));
     return RG_OK;
@@ -186,6 +214,10 @@ extern "C" rg_status rg_gpt_create(rg_ctx* ctx, const rg_gpt_config* cfg, rg_gpt
             delete m;
             return rg_fail(RG_ERR_INVALID_INPUT, "tp_size %d leaves rank %d without vocabulary", T, r);
         }
+    }
+    {
+        const char* pf = getenv("RG_B200_PREFILL");
+        m->use_tc = !(pf && strcmp(pf, "simt") == 0);
     }
     const char* ng = getenv("RG_B200_NO_GRAPH");
     m->use_graph = !(ng && ng[0] == '1');
@@ -371,6 +403,19 @@ extern "C" rg_status rg_gpt_load_params(rg_gpt* m, const float* const* data, con
     RG_TRY(upload_vec(m->lnfb, data[n - 3], D));
     RG_TRY(upload_matrix(m, m->head.W, m->head.ldw, 0, data[n - 2] + m->v0, D, m->Vl, V));  // vocabulary slice
     RG_TRY(upload_vec(m->head.b, data[n - 1] + m->v0, m->Vl));
+    if (m->bf16) {  // K-contiguous copies for the tensor-core prompt pass
+        auto tr = [&](rg_linear& lin) {
+            if (!lin.Wt) return;
+            dim3 grid(rg_cdiv(lin.N, 32), rg_cdiv(lin.K, 32)), block(32, 8);
+            rg_transpose_bf16_kernel<<<grid, block, 0, m->ctx->stream>>>((const __nv_bfloat16*)lin.W, lin.ldw, lin.K, lin.N,
+                                                                        (__nv_bfloat16*)lin.Wt);
+            RG_LAUNCHED(m->ctx);
+        };
+        for (auto& y : m->layers) tr(y.qkv), tr(y.o), tr(y.fc1), tr(y.fc2);
+        tr(m->head);
+        RG_CUDA(cudaGetLastError());
+        RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    }
     m->loaded = true;
     m->pos = 0;
     m->curB = 0;
@@ -384,8 +429,9 @@ static rg_status ensure_rows(rg_gpt* m, size_t rows) {
     if (rows <= m->rowsCap) return RG_OK;
     RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
     dfree(m, m->px), dfree(m, m->pln), dfree(m, m->pqkv), dfree(m, m->pattn), dfree(m, m->ph), dfree(m, m->plast);
-    dfree(m, m->ptp);
+    dfree(m, m->ptp), dfree(m, m->pa16);
     m->px = m->pln = m->pqkv = m->pattn = m->ph = m->plast = m->ptp = nullptr;
+    m->pa16 = nullptr;
     m->rowsCap = 0;
     RG_TRY(dalloc(m, (void**)&m->px, rows * m->D * 4));
     RG_TRY(dalloc(m, (void**)&m->pln, rows * m->D * 4));
@@ -393,6 +439,7 @@ static rg_status ensure_rows(rg_gpt* m, size_t rows) {
     RG_TRY(dalloc(m, (void**)&m->pattn, rows * m->Dl * 4));
     RG_TRY(dalloc(m, (void**)&m->ph, rows * m->Fl * 4));
     if (m->tp_size > 1) RG_TRY(dalloc(m, (void**)&m->ptp, rows * m->D * 4));
+    if (m->bf16 && m->use_tc) RG_TRY(dalloc(m, &m->pa16, std::max<size_t>(rows, 128) * (size_t)std::max(m->D, m->Fl) * 2));
     RG_TRY(dalloc(m, (void**)&m->plast, (size_t)m->Bmax * m->D * 4));
     m->rowsCap = rows;
     return RG_OK;
@@ -423,6 +470,15 @@ static rg_status gemm(rg_gpt* m, const float* A, int M, const rg_linear& lin, fl
     p.C = Cout, p.ldc = ldc < 0 ? lin.N : ldc;
     p.M = M, p.N = lin.N, p.K = lin.K;
     p.bias = with_bias ? lin.b : nullptr, p.res = res, p.ldres = lin.N, p.act = act;
+    if (m->bf16 && m->use_tc && lin.Wt && m->pa16 && M >= 32) {
+        // dense contraction on the tensor cores: bf16 operands (activations rounded on the way in), fp32 accumulate
+        const size_t cnt = (size_t)M * lin.K;
+        rg_to_bf16_kernel<<<rg_cdiv((long long)cnt, 1024), 256, 0, m->ctx->stream>>>(A, (__nv_bfloat16*)m->pa16, cnt);
+        RG_LAUNCHED(m->ctx);
+        rg_status st = rg_gemm_bf16_tc(m->ctx, m->pa16, M, lin.K, lin.Wt, lin.N, Cout, p.ldc, p.bias, res, lin.N, act);
+        if (st == RG_OK) return RG_OK;
+        if (st != RG_ERR_UNSUPPORTED) return st;
+    }
     if (m->bf16) RG_CUDA(rg_gemm_launch<__nv_bfloat16>(m->ctx->stream, p, 1));
     else RG_CUDA(rg_gemm_launch<float>(m->ctx->stream, p, 1));
     RG_LAUNCHED(m->ctx);

@@ -6,6 +6,7 @@ struct rg_mega;  // persistent token-loop kernel state (rg_mega.cu)
 
 struct rg_linear {
     void* W = nullptr;  // [K][ldw] f32 or bf16
+    void* Wt = nullptr;  // bf16 mode: [N][K] copy (K contiguous) for the tensor-core prompt pass
     long long ldw = 0;
     float* b = nullptr;  // [N]
     int K = 0, N = 0;
@@ -57,6 +58,8 @@ struct rg_gpt {
     // prompt-pass buffers, grown on demand
     size_t rowsCap = 0;
     float *px = nullptr, *pln = nullptr, *pqkv = nullptr, *pattn = nullptr, *ph = nullptr, *plast = nullptr;
+    void* pa16 = nullptr;  // bf16 copy of the current GEMM input rows
+    bool use_tc = true;
     float* plogits = nullptr;
     size_t plogitsCap = 0;
 
@@ -66,6 +69,10 @@ struct rg_gpt {
     bool trace_on = false;
     uint32_t epoch = 0;  // token steps run so far by the persistent kernel (tags of its exchange buffers)
 };
+
+// rg_gemm_tc.cu: RG_ERR_UNSUPPORTED when the shape is outside the tensor-core kernel's limits
+rg_status rg_gemm_bf16_tc(rg_ctx* ctx, const void* A16, int M, int K, const void* Wt16, int N, float* C, long long ldc,
+                          const float* bias, const float* res, long long ldres, int act);
 
 // rg_mega.cu
 rg_status rg_mega_create(rg_gpt* m);            // after the weights are on the device
