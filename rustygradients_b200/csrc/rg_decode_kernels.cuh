@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(128) rg_attn_step_kernel(rg_attn_step_args p) 
         const int which = i / HD, d = i - which * HD;
         if (which > 0 && !owns_new) continue;
         const int col = which * p.D + h * HD + d;
-        float v = p.qkv_bias[col];
+        float v = p.qkv_bias ? p.qkv_bias[col] : 0.f;
         const float* pp = p.qkv_parts + (size_t)b * 3 * p.D + col;
         const size_t stride = (size_t)p.B * 3 * p.D;
         for (int k = 0; k < p.nparts; k++) v += pp[k * stride];
@@ -410,4 +410,15 @@ static __global__ void __launch_bounds__(1024) rg_pick_kernel(rg_pick_args p) {
         if (pos + 1 < p.C) p.tokens[(size_t)b * p.C + pos + 1] = (uint32_t)besti;
         if (b == 0) *p.pos_next = pos + 1;
     }
+}
+
+// Merge of the split-context attention partials into finished head outputs:
+// out[b][h*hd + d] = sum_s w_s o_s[d] / sum_s w_s l_s with w_s = exp(m_s - max m).
+static __global__ void rg_attn_merge_kernel(const float* __restrict__ ap, float* __restrict__ out, int B, int H, int hd, int NS) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= B * H * hd) return;
+    rg_vec_in in;
+    in.kind = RG_IN_ATTN, in.ap = ap, in.H = H, in.hd = hd, in.NS = NS;
+    const int b = i / (H * hd), k = i - b * (H * hd);
+    out[i] = rg_vec_in_value(in, B, H * hd, b, k);
 }

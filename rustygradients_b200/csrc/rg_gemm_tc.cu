@@ -19,6 +19,8 @@
 
 #include <cuda.h>
 
+#include <algorithm>
+
 #define TC_BM 128
 #define TC_BN 128
 #define TC_BK 64
@@ -36,6 +38,7 @@ struct tc_epi {
     long long ldres;
     int act;
     int M, N, K;
+    int kb_per_split;  // k-blocks per CTA along z (split-k: partial tiles go to C + z * M * ldc, no epilogue terms)
     int* err;
 };
 
@@ -81,7 +84,8 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
-    const int nkb = e.K / TC_BK;
+    const int kb_begin = blockIdx.z * e.kb_per_split;
+    const int nkb = min(e.kb_per_split, e.K / TC_BK - kb_begin);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; s++) {
@@ -115,12 +119,12 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 asm volatile(
                     "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                         tc_smem(a_dst)),
-                    "l"(&tmA), "r"(kb * TC_BK), "r"(m0), "r"(tc_smem(&full[s]))
+                    "l"(&tmA), "r"((kb_begin + kb) * TC_BK), "r"(m0), "r"(tc_smem(&full[s]))
                     : "memory");
                 asm volatile(
                     "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                         tc_smem(b_dst)),
-                    "l"(&tmB), "r"(kb * TC_BK), "r"(n0), "r"(tc_smem(&full[s]))
+                    "l"(&tmB), "r"((kb_begin + kb) * TC_BK), "r"(n0), "r"(tc_smem(&full[s]))
                     : "memory");
             }
         }
@@ -178,6 +182,7 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float* Cz = e.C + (size_t)blockIdx.z * e.M * e.ldc;
                 if (m < e.M) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
@@ -187,7 +192,7 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                             if (e.bias) v += e.bias[n];
                             if (e.act >= 0) v = rg_apply_act(v, e.act);
                             if (e.res) v += e.res[(long long)m * e.ldres + n];
-                            e.C[(long long)m * e.ldc + n] = v;
+                            Cz[(long long)m * e.ldc + n] = v;
                         }
                     }
                 }
@@ -219,7 +224,29 @@ static rg_status tc_make_map(CUtensorMap* map, const void* base, int rows, int K
     return RG_OK;
 }
 
+// C[m][n] = epi(sum over the k-splits of ws[z][m][n]), fixed order
+static __global__ void tc_splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N, float* __restrict__ C,
+                                               long long ldc, const float* __restrict__ bias, const float* __restrict__ res,
+                                               long long ldres, int act) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)M * N) return;
+    const int m = (int)(i / N), n = (int)(i - (size_t)m * N);
+    float v = 0.f;
+    for (int z = 0; z < splits; z++) v += ws[(size_t)z * M * N + i];
+    if (bias) v += bias[n];
+    if (act >= 0) v = rg_apply_act(v, act);
+    if (res) v += res[(long long)m * ldres + n];
+    C[(long long)m * ldc + n] = v;
+}
+
+static float* g_ws[64];
+static size_t g_ws_bytes[64];
+
 // Returns RG_ERR_UNSUPPORTED (without touching C) when the shape is outside the kernel's limits.
+// With few rows (one M tile) the k range is split over several CTAs so that the weights stream through
+// many SMs at once; the partial tiles are summed, in a fixed order, by a second kernel that also applies
+// the epilogue.  The split-k workspace is allocated on first use per device (not inside a stream capture:
+// the prompt pass, which always runs first, goes through here too).
 rg_status rg_gemm_bf16_tc(rg_ctx* ctx, const void* A16, int M, int K, const void* Wt16, int N, float* C, long long ldc,
                           const float* bias, const float* res, long long ldres, int act) {
     if (K % TC_BK != 0 || K < TC_BK || M <= 0 || N <= 0) return RG_ERR_UNSUPPORTED;
@@ -236,15 +263,56 @@ rg_status rg_gemm_bf16_tc(rg_ctx* ctx, const void* A16, int M, int K, const void
         cudaError_t ea = cudaFuncSetAttribute(rg_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
         if (ea != cudaSuccess) return rg_fail(RG_ERR_BACKEND, "rg_gemm_tc_kernel: %s", cudaGetErrorString(ea));
     }
+    {   // split-k workspace of this device: 64 MiB on the first call (the prompt pass, never inside a capture)
+        const int dev = ctx->device & 63;
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(ctx->stream, &cs);
+        if (!g_ws[dev] && cs == cudaStreamCaptureStatusNone) {
+            if (cudaMalloc(&g_ws[dev], (size_t)64 << 20) == cudaSuccess) g_ws_bytes[dev] = (size_t)64 << 20;
+            else cudaGetLastError();
+        }
+    }
     CUtensorMap tmA, tmB;
     RG_TRY(tc_make_map(&tmA, A16, M, K));
     RG_TRY(tc_make_map(&tmB, Wt16, N, K));
+    const int nkb = K / TC_BK, ntiles = rg_cdiv(N, TC_BN) * rg_cdiv(M, TC_BM);
+    int splits = 1;
+    if (M <= TC_BM && ntiles < ctx->sm_count / 2) splits = std::max(1, std::min(nkb / 2, ctx->sm_count / ntiles));
+    const int kb_per = rg_cdiv(nkb, splits);
+    splits = rg_cdiv(nkb, kb_per);
     tc_epi e;
     e.C = C, e.ldc = ldc, e.bias = bias, e.res = res, e.ldres = ldres, e.act = act, e.M = M, e.N = N, e.K = K;
+    e.kb_per_split = kb_per;
     e.err = ctx->d_flag + 1;
-    dim3 grid(rg_cdiv(N, TC_BN), rg_cdiv(M, TC_BM));
+    if (splits > 1) {
+        const size_t need = (size_t)splits * M * N * 4;
+        const int dev = ctx->device & 63;
+        if (g_ws_bytes[dev] < need) {
+            cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+            cudaStreamIsCapturing(ctx->stream, &cs);
+            if (cs != cudaStreamCaptureStatusNone) {
+                splits = 1, e.kb_per_split = nkb;  // cannot allocate now: run unsplit
+            } else {
+                const size_t want = std::max(need, (size_t)64 << 20);
+                if (g_ws[dev]) cudaFree(g_ws[dev]);
+                g_ws[dev] = nullptr, g_ws_bytes[dev] = 0;
+                if (cudaMalloc(&g_ws[dev], want) == cudaSuccess) g_ws_bytes[dev] = want;
+                else cudaGetLastError(), splits = 1, e.kb_per_split = nkb;
+            }
+        }
+    }
+    if (splits > 1) {
+        e.C = g_ws[ctx->device & 63], e.ldc = N, e.bias = nullptr, e.res = nullptr, e.act = -1;
+    }
+    dim3 grid(rg_cdiv(N, TC_BN), rg_cdiv(M, TC_BM), splits);
     rg_gemm_tc_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(tmA, tmB, e);
     RG_CUDA(cudaGetLastError());
     RG_LAUNCHED(ctx);
+    if (splits > 1) {
+        tc_splitk_reduce_kernel<<<rg_cdiv((long long)M * N, 256), 256, 0, ctx->stream>>>(g_ws[ctx->device & 63], splits, M, N, C, ldc,
+                                                                                         bias, res, ldres, act);
+        RG_CUDA(cudaGetLastError());
+        RG_LAUNCHED(ctx);
+    }
     return RG_OK;
 }

@@ -430,6 +430,7 @@ static rg_status ensure_rows(rg_gpt* m, size_t rows) {
     RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
     dfree(m, m->px), dfree(m, m->pln), dfree(m, m->pqkv), dfree(m, m->pattn), dfree(m, m->ph), dfree(m, m->plast);
     dfree(m, m->ptp), dfree(m, m->pa16);
+    if (m->graph) cudaGraphExecDestroy(m->graph), m->graph = nullptr;  // a captured step may point into the old buffers
     m->px = m->pln = m->pqkv = m->pattn = m->ph = m->plast = m->ptp = nullptr;
     m->pa16 = nullptr;
     m->rowsCap = 0;
@@ -470,7 +471,7 @@ static rg_status gemm(rg_gpt* m, const float* A, int M, const rg_linear& lin, fl
     p.C = Cout, p.ldc = ldc < 0 ? lin.N : ldc;
     p.M = M, p.N = lin.N, p.K = lin.K;
     p.bias = with_bias ? lin.b : nullptr, p.res = res, p.ldres = lin.N, p.act = act;
-    if (m->bf16 && m->use_tc && lin.Wt && m->pa16 && M >= 32) {
+    if (m->bf16 && m->use_tc && lin.Wt && m->pa16 && M >= 8) {
         // dense contraction on the tensor cores: bf16 operands (activations rounded on the way in), fp32 accumulate
         const size_t cnt = (size_t)M * lin.K;
         rg_to_bf16_kernel<<<rg_cdiv((long long)cnt, 1024), 256, 0, m->ctx->stream>>>(A, (__nv_bfloat16*)m->pa16, cnt);
@@ -516,17 +517,24 @@ static rg_status gemm_rowsplit_residual(rg_gpt* m, const float* A, int M, const 
     return RG_OK;
 }
 
+// room for the all-gather of `rows` rows of logits (allocates: never call inside a stream capture)
+static rg_status ensure_gather(rg_gpt* m, int rows) {
+    const size_t per = (size_t)rows * m->Vpad;
+    if (m->tp_size == 1 || per * (m->tp_size + 1) <= m->pgatherCap) return RG_OK;
+    RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    dfree(m, m->pgather);
+    m->pgather = nullptr, m->pgatherCap = 0;
+    RG_TRY(dalloc(m, (void**)&m->pgather, per * (m->tp_size + 1) * 4));
+    m->pgatherCap = per * (m->tp_size + 1);
+    if (m->graph) cudaGraphExecDestroy(m->graph), m->graph = nullptr;
+    return RG_OK;
+}
+
 // logits of `rows` rows: local vocabulary slice, then (tensor parallel) all-gather and re-interleave
 static rg_status head_logits(rg_gpt* m, const float* A, int rows, float* logits) {
     if (m->tp_size == 1) return gemm(m, A, rows, m->head, logits, nullptr, -1);
     const size_t per = (size_t)rows * m->Vpad;
-    if (per * (m->tp_size + 1) > m->pgatherCap) {
-        RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
-        dfree(m, m->pgather);
-        m->pgather = nullptr, m->pgatherCap = 0;
-        RG_TRY(dalloc(m, (void**)&m->pgather, per * (m->tp_size + 1) * 4));
-        m->pgatherCap = per * (m->tp_size + 1);
-    }
+    RG_TRY(ensure_gather(m, rows));
     float* local = m->pgather + per * m->tp_size;
     RG_CUDA(cudaMemsetAsync(local, 0, per * 4, m->ctx->stream));
     RG_TRY(gemm(m, A, rows, m->head, local, nullptr, -1, true, m->Vpad));
@@ -798,6 +806,66 @@ static int enqueue_step(rg_gpt* m, int B) {
     return n;
 }
 
+// Token step for larger batches: with 8 or more sequences a projection is a (small-M) dense contraction, so the step
+// runs on the prompt-pass kernels (LayerNorm rows, GEMM - tensor cores in bf16 mode -, row-split all-reduce when tensor
+// parallel) around the KV-cache attention.  Returns the number of launches, or -1 on error.
+static int enqueue_step_rows(rg_gpt* m, int B) {
+    cudaStream_t s = m->ctx->stream;
+    const uint64_t l0 = m->ctx->launches;
+    const int D = m->D, act = m->cfg.activation;
+    if (m->bf16)
+        rg_embed_step_kernel<__nv_bfloat16><<<B, 128, 0, s>>>(m->tokens, m->C, (const __nv_bfloat16*)m->wte,
+                                                              (const __nv_bfloat16*)m->wpe, D, m->ldt, m->px, m->d_pos_next,
+                                                              m->d_pos);
+    else
+        rg_embed_step_kernel<float><<<B, 128, 0, s>>>(m->tokens, m->C, (const float*)m->wte, (const float*)m->wpe, D, m->ldt,
+                                                      m->px, m->d_pos_next, m->d_pos);
+    RG_LAUNCHED(m->ctx);
+    for (int l = 0; l < m->L; l++) {
+        rg_layer& y = m->layers[l];
+        rg_ln_rows_kernel<<<rg_cdiv(B, 8), 256, 0, s>>>(m->px, D, y.ln1g, y.ln1b, m->pln, (size_t)B, D, 1e-5f);
+        RG_LAUNCHED(m->ctx);
+        if (gemm(m, m->pln, B, y.qkv, m->pqkv, nullptr, -1) != RG_OK) return -1;
+        {   // attention over the cache: q, k, v rows are finished values here (one "partial", no bias left to add)
+            rg_attn_step_args a;
+            a.qkv_parts = m->pqkv, a.nparts = 1, a.qkv_bias = nullptr;
+            a.kcache = m->kc + (size_t)l * m->kv_layer_bytes, a.vcache = m->vc + (size_t)l * m->kv_layer_bytes;
+            a.ap = m->ap, a.pos = m->d_pos;
+            a.B = B, a.H = m->Hl, a.C = m->C, a.D = m->Dl, a.NS = m->NS;
+            a.scale = 1.f / sqrtf((float)m->hd);
+            dim3 grid(m->NS, m->Hl, B);
+            if (m->bf16) {
+                if (m->hd == 32) rg_attn_step_kernel<__nv_bfloat16, 32><<<grid, 128, 0, s>>>(a);
+                else if (m->hd == 64) rg_attn_step_kernel<__nv_bfloat16, 64><<<grid, 128, 0, s>>>(a);
+                else rg_attn_step_kernel<__nv_bfloat16, 128><<<grid, 128, 0, s>>>(a);
+            } else {
+                if (m->hd == 32) rg_attn_step_kernel<float, 32><<<grid, 128, 0, s>>>(a);
+                else if (m->hd == 64) rg_attn_step_kernel<float, 64><<<grid, 128, 0, s>>>(a);
+                else rg_attn_step_kernel<float, 128><<<grid, 128, 0, s>>>(a);
+            }
+            rg_attn_merge_kernel<<<rg_cdiv(B * m->Dl, 256), 256, 0, s>>>(m->ap, m->pattn, B, m->Hl, m->hd, m->NS);
+            m->ctx->launches += 2;
+        }
+        if (gemm_rowsplit_residual(m, m->pattn, B, y.o, m->px) != RG_OK) return -1;
+        rg_ln_rows_kernel<<<rg_cdiv(B, 8), 256, 0, s>>>(m->px, D, y.ln2g, y.ln2b, m->pln, (size_t)B, D, 1e-5f);
+        RG_LAUNCHED(m->ctx);
+        if (gemm(m, m->pln, B, y.fc1, m->ph, nullptr, act) != RG_OK) return -1;
+        if (gemm_rowsplit_residual(m, m->ph, B, y.fc2, m->px) != RG_OK) return -1;
+    }
+    rg_ln_rows_kernel<<<rg_cdiv(B, 8), 256, 0, s>>>(m->px, D, m->lnfg, m->lnfb, m->plast, (size_t)B, D, 1e-5f);
+    RG_LAUNCHED(m->ctx);
+    if (head_logits(m, m->plast, B, m->logits) != RG_OK) return -1;
+    rg_pick_args pa;
+    pa.parts = m->logits, pa.nparts = 1, pa.bias = nullptr, pa.logits = m->logits;
+    pa.tokens = m->tokens, pa.picks = m->picks, pa.pos = m->d_pos, pa.pos_next = m->d_pos_next;
+    pa.B = B, pa.V = m->V, pa.C = m->C;
+    rg_pick_kernel<<<B, 1024, 0, s>>>(pa);
+    RG_LAUNCHED(m->ctx);
+    const int n = (int)(m->ctx->launches - l0);
+    m->ctx->launches = l0;  // the caller accounts for the launches (once per replay when captured)
+    return n;
+}
+
 static rg_status step_ready(rg_gpt* m, size_t steps) {
     if (!m->cfg.causal)
         return rg_fail(RG_ERR_UNSUPPORTED,
@@ -821,9 +889,16 @@ static rg_status run_steps(rg_gpt* m, size_t steps) {
         }
         if (st != RG_ERR_UNSUPPORTED) return st;
     }
+    const bool rows_path = (m->bf16 && m->use_tc) ? B >= 8 : B >= 32;  // where a projection is worth a GEMM launch
+    if (rows_path) {  // before capture: may allocate
+        RG_TRY(ensure_rows(m, (size_t)std::max(B, 128)));
+        RG_TRY(ensure_gather(m, B));
+    }
     if (!m->use_graph) {
         for (size_t i = 0; i < steps; i++) {
-            m->ctx->launches += enqueue_step(m, B);
+            const int n = rows_path ? enqueue_step_rows(m, B) : enqueue_step(m, B);
+            if (n < 0) return RG_ERR_BACKEND;
+            m->ctx->launches += n;
             RG_CUDA(cudaGetLastError());
         }
     } else {
@@ -831,8 +906,12 @@ static rg_status run_steps(rg_gpt* m, size_t steps) {
             if (m->graph) cudaGraphExecDestroy(m->graph), m->graph = nullptr;
             cudaGraph_t gr = nullptr;
             RG_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-            m->kernels_per_step = enqueue_step(m, B);
+            m->kernels_per_step = rows_path ? enqueue_step_rows(m, B) : enqueue_step(m, B);
             cudaError_t e = cudaStreamEndCapture(s, &gr);
+            if (m->kernels_per_step < 0) {
+                if (gr) cudaGraphDestroy(gr);
+                return RG_ERR_BACKEND;
+            }
             if (e != cudaSuccess) return rg_fail(RG_ERR_BACKEND, "graph capture failed: %s", cudaGetErrorString(e));
             e = cudaGraphInstantiate(&m->graph, gr, 0);
             cudaGraphDestroy(gr);

@@ -24,8 +24,22 @@ static __global__ void __launch_bounds__(256) rg_ln_rows_kernel(const float* __r
     const int lane = threadIdx.x & 31;
     const float* xr = x + row * ldx;
     float* yr = y + row * n;
-    rg_welford w = {0.f, 0.f, 0.f};
-    for (int i = lane; i < n; i += 32) rg_welford_add(w, xr[i]);
+    // per-lane Welford over a strided subset costs a division per element; a lane's (count, mean, M2) is
+    // obtained instead from shifted sums with c = x[0] (exactly the quantities Welford maintains), then the
+    // 32 lanes are merged pairwise with Chan's formula as before
+    const float c = xr[0];
+    float s1 = 0.f, s2 = 0.f, cnt = 0.f;
+    for (int i = lane; i < n; i += 32) {
+        const float d = xr[i] - c;
+        s1 += d;
+        s2 = fmaf(d, d, s2);
+        cnt += 1.f;
+    }
+    rg_welford w;
+    w.n = cnt;
+    const float m1 = cnt > 0.f ? s1 / cnt : 0.f;
+    w.mean = c + m1;
+    w.m2 = fmaxf(s2 - s1 * m1, 0.f);
     w = rg_welford_warp(w);
     const float inv = 1.f / sqrtf(w.m2 / (float)n + eps);
     for (int i = lane; i < n; i += 32) yr[i] = (xr[i] - w.mean) * inv * gamma[i] + beta[i];
