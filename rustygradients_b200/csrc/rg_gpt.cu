@@ -440,6 +440,10 @@ static rg_status ensure_rows(rg_gpt* m, size_t rows) {
     RG_TRY(dalloc(m, (void**)&m->pattn, rows * m->Dl * 4));
     RG_TRY(dalloc(m, (void**)&m->ph, rows * m->Fl * 4));
     if (m->tp_size > 1) RG_TRY(dalloc(m, (void**)&m->ptp, rows * m->D * 4));
+    if (!m->pws) {  // 32 MiB: enough to split the k range of every few-row projection of the supported shapes
+        m->pwsFloats = (size_t)8 << 20;
+        RG_TRY(dalloc(m, (void**)&m->pws, m->pwsFloats * 4));
+    }
     if (m->bf16 && m->use_tc) RG_TRY(dalloc(m, &m->pa16, std::max<size_t>(rows, 128) * (size_t)std::max(m->D, m->Fl) * 2));
     RG_TRY(dalloc(m, (void**)&m->plast, (size_t)m->Bmax * m->D * 4));
     m->rowsCap = rows;
@@ -480,9 +484,10 @@ static rg_status gemm(rg_gpt* m, const float* A, int M, const rg_linear& lin, fl
         if (st == RG_OK) return RG_OK;
         if (st != RG_ERR_UNSUPPORTED) return st;
     }
-    if (m->bf16) RG_CUDA(rg_gemm_launch<__nv_bfloat16>(m->ctx->stream, p, 1));
-    else RG_CUDA(rg_gemm_launch<float>(m->ctx->stream, p, 1));
-    RG_LAUNCHED(m->ctx);
+    int nl = 1;
+    if (m->bf16) RG_CUDA(rg_gemm_launch<__nv_bfloat16>(m->ctx->stream, p, 1, m->pws, m->pwsFloats, m->ctx->sm_count, &nl));
+    else RG_CUDA(rg_gemm_launch<float>(m->ctx->stream, p, 1, m->pws, m->pwsFloats, m->ctx->sm_count, &nl));
+    m->ctx->launches += nl;
     return RG_OK;
 }
 

@@ -59,6 +59,8 @@ struct rg_gpt {
     size_t rowsCap = 0;
     float *px = nullptr, *pln = nullptr, *pqkv = nullptr, *pattn = nullptr, *ph = nullptr, *plast = nullptr;
     void* pa16 = nullptr;  // bf16 copy of the current GEMM input rows
+    float* pws = nullptr;  // split-k workspace of the CUDA-core GEMM
+    size_t pwsFloats = 0;
     bool use_tc = true;
     float* plogits = nullptr;
     size_t plogitsCap = 0;
