@@ -893,6 +893,8 @@ static rg_status run_steps(rg_gpt* m, size_t steps) {
             return RG_OK;
         }
         if (st != RG_ERR_UNSUPPORTED) return st;
+        // the model does not fit the persistent kernel, or its CTAs cannot all be resident at once (a GPU shared
+        // with other work): the CUDA-graph step below computes the same thing
     }
     const bool rows_path = (m->bf16 && m->use_tc) ? B >= 8 : B >= 32;  // where a projection is worth a GEMM launch
     if (rows_path) {  // before capture: may allocate

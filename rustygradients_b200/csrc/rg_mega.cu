@@ -1325,6 +1325,11 @@ rg_status rg_mega_run(rg_gpt* m, int B, size_t pos0, size_t n_steps) {
         else if (B == 2) e = mg_launch<__nv_bfloat16, 2, 2>(m, g, prm);
         else e = mg_launch<__nv_bfloat16, 4, 1>(m, g, prm);
     }
+    if (e == cudaErrorCooperativeLaunchTooLarge || e == cudaErrorLaunchOutOfResources) {
+        cudaGetLastError();
+        m->use_mega = false;  // its CTAs cannot be co-resident here: use the CUDA-graph step from now on
+        return RG_ERR_UNSUPPORTED;
+    }
     if (e != cudaSuccess)
         return rg_fail(RG_ERR_BACKEND, "persistent token-loop kernel launch failed: %s", cudaGetErrorString(e));
     m->epoch += (uint32_t)n_steps;

@@ -251,3 +251,28 @@ def test_topk_temperature_sampling(backend):
     mr = model_for(backend, cfg, params, causal=False, act="relu", max_batch=4)
     a = mr.generate(prompt, 6, temperature=0.8, top_k=10, seed=4)
     assert a.shape == (B, 6) and np.array_equal(a, mr.generate(prompt, 6, temperature=0.8, top_k=10, seed=4))
+
+
+# ---- the two token-step implementations compute the same thing
+def test_persistent_kernel_equals_graph_step(backend, monkeypatch):
+    cfg = O.GptConfig(96, 1024, 3, 4, 256)
+    params = O.make_params(cfg, 21, stress=True)
+    for B in (1, 2, 4):
+        prompt = O.make_prompt(cfg, 21 + B, B, 17)
+        monkeypatch.delenv("RG_B200_DECODE", raising=False)
+        a = model_for(backend, cfg, params, max_batch=4)        # persistent cooperative kernel
+        monkeypatch.setenv("RG_B200_DECODE", "graph")
+        b = model_for(backend, cfg, params, max_batch=4)        # CUDA-graph step (the variable is read at load time)
+        monkeypatch.delenv("RG_B200_DECODE", raising=False)
+        ids = np.concatenate([prompt, a.generate(prompt, 40)], 1)
+        la, pa = teacher_forced(a, ids, 17)
+        lb, pb = teacher_forced(b, ids, 17)
+        assert np.abs(la - lb).max() <= 2e-5
+        assert np.array_equal(pa, la.argmax(-1)) and np.array_equal(pb, lb.argmax(-1))
+        l0 = backend.launch_count
+        a.rewind(17)
+        a.decode_run(30)
+        backend.synchronize()
+        assert backend.launch_count - l0 <= 3                    # one launch for 30 token steps
+        tr_rows = a.read_trace()
+        assert tr_rows.shape[1] == 10
