@@ -187,10 +187,11 @@ RG_API rg_status rg_gpt_tp_init(rg_gpt* m, const uint8_t id[128]);
 
 /* Profiling aid of the persistent token-loop kernel (engine-only, nothing to mirror in the
  * reference): when enabled, the last token step of every rg_gpt_decode_run records device
- * timestamps per CTA and stage.  rg_gpt_trace_read returns rows of 10 uint64:
+ * timestamps per CTA and stage.  rg_gpt_trace_read returns rows of 12 uint64:
  * cta, op index, stage (0 QKV, 1 attention, 2 out-proj, 3 FC1, 4 FC2, 5 LM head), layer,
  * ns timestamps (stage start, input vector ready, dot products done, outputs stored), then SM
- * cycles spent waiting for weight/KV chunks and for the input vector. */
+ * cycles spent waiting for weight/KV chunks and for the input vector, then two more ns timestamps:
+ * all input words valid, chunk loop finished (0 where a stage does not record them). */
 RG_API rg_status rg_gpt_trace_enable(rg_gpt* m, int on);
 RG_API rg_status rg_gpt_trace_read(rg_gpt* m, uint64_t* out, size_t cap_rows, size_t* n_rows);
 

@@ -32,11 +32,12 @@
 
 #define MG_THREADS 256
 #define MG_SLOT_BYTES 32768
+#define MG_ATTN_PASSES (MG_SLOT_BYTES / 4096)  // rows of a full K/V chunk that one lane group of one warp handles
 #define MG_SPIN_LIMIT (1u << 21)
 #define MG_BMAX 4
 
 enum { MG_QKV = 0, MG_ATTN = 1, MG_OPROJ = 2, MG_FC1 = 3, MG_FC2 = 4, MG_HEAD = 5 };
-enum { MG_FIRST = 1, MG_LAST = 2, MG_LNPRE = 4 };  // LNPRE: the op's first chunk is [gamma | beta] of its LayerNorm
+enum { MG_FIRST = 1, MG_LAST = 2 };
 
 typedef unsigned long long mg_word;  // (tag << 32) | payload bits
 
@@ -52,7 +53,7 @@ struct mg_op {
 
 // One entry of a CTA's copy schedule for a token step.
 struct mg_cdesc {
-    long long src;  // kind 0: byte offset into the packed weights; 1: byte offset into the LayerNorm block; 2: op index
+    long long src;  // kind 0: byte offset into the packed weights; 2: index of an attention op (its K/V slices)
     int bytes;
     int kind;
 };
@@ -63,7 +64,6 @@ struct mg_params {
     const mg_cdesc* cds;  // per-CTA copy schedule of one token step
     const int* cd_off;
     const unsigned char* wpack;
-    const float* lnpack;  // [2L+1][2][D]: gamma | beta of ln1, ln2 per layer, then the final LayerNorm
     unsigned long long* trace;  // optional [G][max_ops][4] timestamps of the last token step
 
     const void *wte, *wpe;
@@ -82,7 +82,6 @@ struct mg_params {
     int nslot, max_ops, max_cd, res_cap, n_pick_ctas;
     int poll_sleep;
     int S;  // CTAs that share one (sequence, head) in the attention stage, each a slice of the context
-    int res_q0, res_nq;  // residual slice = column groups [res_q0, res_q0 + res_nq) of the N=D stages (per CTA: via ops)
     float scale;
 };
 
@@ -99,7 +98,6 @@ struct rg_mega {
     int max_cd = 0;
     unsigned char* d_wpack = nullptr;
     size_t wpack_bytes = 0;
-    float* d_lnpack = nullptr;
     unsigned long long* d_trace = nullptr;
     mg_word *buf_qkv = nullptr, *buf_a = nullptr, *buf_xc = nullptr, *buf_h = nullptr, *buf_xe = nullptr,
             *buf_pick = nullptr;
@@ -107,7 +105,6 @@ struct rg_mega {
     mg_word* buf_base = nullptr;
     int* d_abort = nullptr;
     int max_ops = 0, res_cap = 0, n_pick_ctas = 0, S = 1;
-    int nq_max[3] = {0, 0, 0};  // column groups per op for B = 1, 2, 4
     int nslot = 0;
     size_t smem_bytes = 0;
     int built_for_B = 0;
@@ -298,7 +295,6 @@ __device__ void mg_producer(const mg_params& p, const mg_cdesc* cd, int ncd, con
                 const unsigned char* src;
                 uint32_t bytes;
                 if (d.kind == 0) src = p.wpack + d.src, bytes = (uint32_t)d.bytes;
-                else if (d.kind == 1) src = reinterpret_cast<const unsigned char*>(p.lnpack) + d.src, bytes = (uint32_t)d.bytes;
                 else {
                     const int jj = j >> 1;  // K rows of a range, then V rows of the same range
                     const int rows = min(rc, arows - jj * rc);
@@ -427,7 +423,8 @@ struct mg_halver {
 // mean coefficient.
 template <typename WT, int B, int NQA, int UB, bool TRACE>
 __device__ __forceinline__ void mg_group_dots(const mg_op& op, mg_cons& ring, mg_ctl& ctl, const float* xs, int XLEN,
-                                              float* red, float& t0, float& t1, long long& wait_cyc) {
+                                              float* red, float& t0, float& t1, long long& wait_cyc,
+                                              unsigned long long* tr_loop) {
     constexpr int UV = UB / (int)sizeof(WT);  // columns per unit
     constexpr int NV = B * NQA * UV;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -474,6 +471,7 @@ __device__ __forceinline__ void mg_group_dots(const mg_op& op, mg_cons& ring, mg
         }
         mg_ring_release(ring);
     }
+    if (TRACE && tr_loop) *tr_loop = mg_globaltimer();
     int base = 0, count = 0;
     mg_halver<NV, 16>::run(acc, lane, base, count);
     if (mg_halver<NV, 16>::writer(lane)) {
@@ -536,6 +534,8 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
     sp += MG_BMAX * 4;
     int* s_flags = reinterpret_cast<int*>(sp);  // [0] consumer progress, [1] dead
     sp += 4 * 4;
+    float* awts = reinterpret_cast<float*>(sp);  // [256] normalised weights of the attention records
+    sp += 256 * 4;
     float* pickbuf = reinterpret_cast<float*>(sp);  // [n_pick_ctas * B * 2]
 
     const int op0 = p.cta_off[cta];
@@ -604,13 +604,39 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
         float my_best = -INFINITY;
         int my_besti = 0x7fffffff;
 
-        for (int oi = 0; oi < nops; oi++) {
-            if (mg_csync_or(ctl.dead)) {
-                ctl.dead = true;
-                break;
+        // Deferred append of the new k, v row (held in sqkv since the attention op).  Generic-proxy stores that later
+        // tokens read with bulk copies, possibly from another CTA: proxy fence + gpu-scope fence here, and every CTA
+        // fences again after it has read the token's picks (which depend on this CTA's later stores).
+        int append_layer = -1, append_b = 0, append_h = 0;
+        auto flush_append = [&]() {
+            if (append_layer < 0) return;
+            const int HD = p.hd;
+            const size_t row = (((size_t)append_b * p.H + append_h) * p.C + pos) * HD;
+            WT* kdst = reinterpret_cast<WT*>(p.kc + (size_t)append_layer * p.kv_layer_bytes) + row;
+            WT* vdst = reinterpret_cast<WT*>(p.vc + (size_t)append_layer * p.kv_layer_bytes) + row;
+            for (int i = tid; i < 2 * HD; i += MG_THREADS) {
+                const int which = i / HD, d = i - which * HD;
+                const float v = sqkv[(which + 1) * 128 + d];
+                WT* dst = which == 0 ? kdst : vdst;
+                if (KVS == 4) reinterpret_cast<float*>(dst)[d] = v;
+                else reinterpret_cast<__nv_bfloat16*>(dst)[d] = __float2bfloat16_rn(v);
             }
-            if (tid == 0) *reinterpret_cast<volatile int*>(s_flags) = t * nops + oi;  // the producer reads this
+            mg_fence_proxy_async();
+            __threadfence();
+            append_layer = -1;
+        };
+        int prev_type = MG_ATTN;  // forces a barrier before the first op of the token
+        for (int oi = 0; oi < nops; oi++) {
             const mg_op op = ops[oi];
+            // A barrier at the start of an op is only needed when shared memory of the previous op could still be in
+            // use: attention scratch (either side), or a further group of the same stage (the `red` array).  Between
+            // two projection stages the barrier after the previous dot products already ordered everything.
+            if (op.type == MG_ATTN || prev_type == MG_ATTN || !(op.flags & MG_FIRST)) {
+                if (mg_csync_or(ctl.dead)) ctl.dead = true;
+            }
+            if (ctl.dead) break;
+            prev_type = op.type;
+            if (tid == 0) *reinterpret_cast<volatile int*>(s_flags) = t * nops + oi;  // the producer reads this
             const uint32_t tag = tagbase + (uint32_t)op.layer + 1u;
             const bool tracing = TRACE && p.trace != nullptr && t == p.n_steps - 1 && tid == 0;
             unsigned long long* tr = tracing ? p.trace + ((size_t)cta * p.max_ops + oi) * 8 : nullptr;
@@ -618,6 +644,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
             if (tracing) tr[0] = mg_globaltimer();
 
             if (op.type == MG_ATTN) {
+                flush_append();  // sqkv is about to be reused
                 // =================== attention of (sequence b, head h) ===================
                 // One CTA per (sequence, head).  Each warp owns every 8th group of cached rows and keeps its
                 // own running softmax (max m, sum l, output o); K rows and V rows of the same positions arrive
@@ -648,7 +675,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                     sqkv[which * 128 + d] = v;
                 }
                 mg_csync();
-                const int rc = mg_attn_rows_per_chunk(HD, KVS);  // = 8 passes of the 8 warps
+                const int rc = mg_attn_rows_per_chunk(HD, KVS);  // = MG_ATTN_PASSES passes of the 8 warps
                 const int nk = (arows + rc - 1) / rc;
                 if (tracing) tr[1] = mg_globaltimer();
                 float qf[VEC];
@@ -659,7 +686,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                 for (int j = 0; j < VEC; j++) acc[j] = 0.f;
                 for (int j = 0; j < nk; j++) {
                     const int rows = min(rc, arows - j * rc);
-                    float sreg[8];
+                    float sreg[MG_ATTN_PASSES];
                     {   // scores of this warp's rows of the chunk: 8 independent rows in flight per lane group.
                         // Rows past the end are read from the last valid row and masked: no branches.
                         long long c0 = 0;
@@ -667,7 +694,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                         const unsigned char* slot = mg_ring_wait(ring, ctl);
                         if constexpr (TRACE) wait_cyc += clock64() - c0;
 #pragma unroll
-                        for (int u = 0; u < 8; u++) {
+                        for (int u = 0; u < MG_ATTN_PASSES; u++) {
                             const int rr = min((u * NWARP + warp) * RPW + g2, rows - 1);
                             float kf[VEC];
                             mg_vec<WT>::unpack(*reinterpret_cast<const uint4*>(slot + ((size_t)rr * LPR + sub) * 16), kf);
@@ -678,13 +705,13 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                         }
                         for (int o = LPR >> 1; o > 0; o >>= 1) {
 #pragma unroll
-                            for (int u = 0; u < 8; u++) sreg[u] += __shfl_xor_sync(RG_FULL_MASK, sreg[u], o);
+                            for (int u = 0; u < MG_ATTN_PASSES; u++) sreg[u] += __shfl_xor_sync(RG_FULL_MASK, sreg[u], o);
                         }
                         mg_ring_release(ring);
                     }
                     float cm = -INFINITY;
 #pragma unroll
-                    for (int u = 0; u < 8; u++) {
+                    for (int u = 0; u < MG_ATTN_PASSES; u++) {
                         const int rr = (u * NWARP + warp) * RPW + g2;
                         sreg[u] = rr < rows ? sreg[u] * p.scale : -INFINITY;
                         cm = fmaxf(cm, sreg[u]);
@@ -695,7 +722,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                     m = mn;
                     float psum = 0.f;
 #pragma unroll
-                    for (int u = 0; u < 8; u++) {
+                    for (int u = 0; u < MG_ATTN_PASSES; u++) {
                         sreg[u] = __expf(sreg[u] - msafe);  // masked rows: exp(-inf) = 0
                         psum += sreg[u];
                     }
@@ -708,7 +735,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                         const unsigned char* slot = mg_ring_wait(ring, ctl);
                         if constexpr (TRACE) wait_cyc += clock64() - c0;
 #pragma unroll
-                        for (int u = 0; u < 8; u++) {
+                        for (int u = 0; u < MG_ATTN_PASSES; u++) {
                             const int rr = min((u * NWARP + warp) * RPW + g2, rows - 1);
                             float vf[VEC];
                             mg_vec<WT>::unpack(*reinterpret_cast<const uint4*>(slot + ((size_t)rr * LPR + sub) * 16), vf);
@@ -756,21 +783,9 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                     }
                 }
                 if (is_last) {
-                    // append k, v at row pos, off the critical path.  Generic-proxy stores that later tokens read
-                    // with bulk copies, possibly from another CTA: proxy fence + gpu-scope fence here, and every
-                    // CTA fences again after it has read the token's picks (which depend on this CTA's later stores).
-                    const size_t row = (((size_t)b * p.H + h) * p.C + pos) * HD;
-                    WT* kdst = reinterpret_cast<WT*>(p.kc + (size_t)op.layer * p.kv_layer_bytes) + row;
-                    WT* vdst = reinterpret_cast<WT*>(p.vc + (size_t)op.layer * p.kv_layer_bytes) + row;
-                    for (int i = tid; i < 2 * HD; i += MG_THREADS) {
-                        const int which = i / HD, d = i - which * HD;
-                        const float v = sqkv[(which + 1) * 128 + d];
-                        WT* dst = which == 0 ? kdst : vdst;
-                        if (KVS == 4) reinterpret_cast<float*>(dst)[d] = v;
-                        else reinterpret_cast<__nv_bfloat16*>(dst)[d] = __float2bfloat16_rn(v);
-                    }
-                    mg_fence_proxy_async();
-                    __threadfence();
+                    // k, v of the new row still have to be appended to the cache: not now, the out-projection is waiting
+                    // for this CTA; flush_append() runs after the next projection's outputs are on their way
+                    append_layer = op.layer, append_b = b, append_h = h;
                 }
                 if (tracing) tr[3] = mg_globaltimer(), tr[4] = (unsigned long long)wait_cyc, tr[5] = 0;
                 continue;
@@ -798,9 +813,10 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                         if (local) {
                             for (int i = tid; i < n_in; i += MG_THREADS) xs[b * XLEN + i] = xemb[b * p.D + i];
                         } else {
-                            mg_fetch<8>(src + (size_t)b * n_in, n_in, in_tag, xs + b * XLEN, ctl);
+                            mg_fetch<2>(src + (size_t)b * n_in, n_in, in_tag, xs + b * XLEN, ctl);  // D values: <= 2 pairs per thread up to D = 1024
                         }
                     }
+                    if (tracing) tr[6] = mg_globaltimer();
                     mg_csync();
 #pragma unroll
                     for (int b = 0; b < B; b++) {
@@ -822,25 +838,54 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                     const int rec = p.hd + 2, nrec = B * p.H * p.S * rec;
                     mg_fetch<8>(p.buf_a, nrec, in_tag, xs, ctl);
                     mg_csync();
+                    if (tracing) tr[6] = mg_globaltimer();
                     float* vec = xs + ((nrec + 3) & ~3);
-                    for (int i = tid; i < B * p.D; i += MG_THREADS) {
-                        const int b = i / p.D, k = i - b * p.D;
-                        const int hh = k / p.hd, d = k - hh * p.hd;
-                        const float* r0 = xs + ((size_t)(b * p.H + hh) * p.S) * rec;
-                        float M = -INFINITY;
-                        for (int sp2 = 0; sp2 < p.S; sp2++) M = fmaxf(M, r0[sp2 * rec]);
-                        float num = 0.f, den = 0.f;
-                        for (int sp2 = 0; sp2 < p.S; sp2++) {
-                            const float w = __expf(r0[sp2 * rec] - M);  // 0 for an empty slice (its max is -inf)
-                            num = fmaf(w, r0[sp2 * rec + 2 + d], num);
-                            den = fmaf(w, r0[sp2 * rec + 1], den);
+                    // normalised weight of every record, once per (sequence, head, slice): w_s = exp(m_s - M) / sum_s exp(m_s - M) l_s
+                    const int nw = B * p.H * p.S;
+                    // (4 lanes per (sequence, head): slices in parallel, max and sum by two shuffles each; S <= 4)
+                    for (int i0 = 0; i0 < B * p.H; i0 += MG_THREADS / 4) {
+                        const int i = i0 + (tid >> 2), sp2 = tid & 3;
+                        const bool on = i < B * p.H && sp2 < p.S;
+                        const float* r0 = xs + ((size_t)(on ? i : 0) * p.S + (on ? sp2 : 0)) * rec;
+                        const float ms = on ? r0[0] : -INFINITY, ls = on ? r0[1] : 0.f;
+                        float M = fmaxf(ms, __shfl_xor_sync(RG_FULL_MASK, ms, 1));
+                        M = fmaxf(M, __shfl_xor_sync(RG_FULL_MASK, M, 2));
+                        const float w = on ? __expf(ms - M) : 0.f;
+                        float den = w * ls;
+                        den += __shfl_xor_sync(RG_FULL_MASK, den, 1);
+                        den += __shfl_xor_sync(RG_FULL_MASK, den, 2);
+                        if (on && i * p.S + sp2 < 256) awts[i * p.S + sp2] = __fdividef(w, den);  // 0 for an empty slice
+                    }
+                    mg_csync();
+                    const int hshift = 31 - __clz(p.hd);  // head_dim is 32, 64 or 128
+#pragma unroll
+                    for (int b = 0; b < B; b++) {
+                        for (int k = tid; k < p.D; k += MG_THREADS) {
+                            const int hh = k >> hshift, d = k & (p.hd - 1);
+                            const int wi = (b * p.H + hh) * p.S;
+                            const float* r0 = xs + (size_t)wi * rec + 2 + d;
+                            float o = 0.f;
+                            if (nw <= 256) {
+                                for (int sp2 = 0; sp2 < p.S; sp2++) o = fmaf(awts[wi + sp2], r0[sp2 * rec], o);
+                            } else {  // more records than the weight array holds: recompute the weights in place
+                                const float* rr = xs + (size_t)wi * rec;
+                                float M = -INFINITY, den = 0.f;
+                                for (int sp2 = 0; sp2 < p.S; sp2++) M = fmaxf(M, rr[sp2 * rec]);
+                                for (int sp2 = 0; sp2 < p.S; sp2++) {
+                                    const float w = __expf(rr[sp2 * rec] - M);
+                                    o = fmaf(w, r0[sp2 * rec], o);
+                                    den = fmaf(w, rr[sp2 * rec + 1], den);
+                                }
+                                o = __fdividef(o, den);
+                            }
+                            vec[b * p.D + k] = o;
                         }
-                        vec[i] = __fdividef(num, den);
                     }
                     mg_csync();
                 } else {
 #pragma unroll
                     for (int b = 0; b < B; b++) mg_fetch<8>(src + (size_t)b * n_in, n_in, in_tag, xs + b * XLEN, ctl);
+                    if (tracing) tr[6] = mg_globaltimer();
                     mg_csync();
                 }
                 if constexpr (TRACE) poll_cyc += clock64() - c0;
@@ -853,25 +898,25 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
             if (op.type == MG_OPROJ) xin = xs + ((B * p.H * p.S * (p.hd + 2) + 3) & ~3), xstride = p.D;
             if (op.uv == VEC) {
                 switch (op.nq) {
-                    case 1: mg_group_dots<WT, B, 1, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
-                    case 2: if constexpr (NQ >= 2) mg_group_dots<WT, B, 2, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
-                    case 3: if constexpr (NQ >= 3) mg_group_dots<WT, B, 3, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
-                    case 4: if constexpr (NQ >= 4) mg_group_dots<WT, B, 4, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
-                    case 5: if constexpr (NQ >= 5) mg_group_dots<WT, B, 5, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
-                    default: if constexpr (NQ >= 6) mg_group_dots<WT, B, 6, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                    case 1: mg_group_dots<WT, B, 1, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
+                    case 2: if constexpr (NQ >= 2) mg_group_dots<WT, B, 2, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
+                    case 3: if constexpr (NQ >= 3) mg_group_dots<WT, B, 3, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
+                    case 4: if constexpr (NQ >= 4) mg_group_dots<WT, B, 4, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
+                    case 5: if constexpr (NQ >= 5) mg_group_dots<WT, B, 5, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
+                    default: if constexpr (NQ >= 6) mg_group_dots<WT, B, 6, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
                 }
             } else {  // 8-byte units (N = D stages): half as many columns per unit, twice as many units allowed
                 switch (op.nq) {
-                    case 1: mg_group_dots<WT, B, 1, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
-                    case 2: mg_group_dots<WT, B, 2, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
-                    case 3: if constexpr (NQ >= 2) mg_group_dots<WT, B, 3, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
-                    case 4: if constexpr (NQ >= 2) mg_group_dots<WT, B, 4, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
-                    case 5: if constexpr (NQ >= 3) mg_group_dots<WT, B, 5, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
-                    default: if constexpr (NQ >= 3) mg_group_dots<WT, B, 6, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc); break;
+                    case 1: mg_group_dots<WT, B, 1, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
+                    case 2: mg_group_dots<WT, B, 2, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
+                    case 3: if constexpr (NQ >= 2) mg_group_dots<WT, B, 3, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
+                    case 4: if constexpr (NQ >= 2) mg_group_dots<WT, B, 4, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
+                    case 5: if constexpr (NQ >= 3) mg_group_dots<WT, B, 5, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
+                    default: if constexpr (NQ >= 3) mg_group_dots<WT, B, 6, 8, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
                 }
             }
-            mg_csync();
-            if (stats_pending) {
+            if (mg_csync_or(ctl.dead)) ctl.dead = true;  // uniform from here on
+            if (stats_pending && tid < NOUT) {
                 // shifted sums of all warps -> mean and 1/sqrt(biased variance + eps) (src/ops/norm.rs:41-52)
 #pragma unroll
                 for (int b = 0; b < B; b++) {
@@ -883,8 +928,8 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                     mu[b] = xs[b * XLEN] + m1;
                     rstd[b] = rsqrtf(fmaxf(fmaf(-m1, m1, t2s * rn), 0.f) + 1e-5f);
                 }
-                stats_pending = false;
             }
+            stats_pending = false;
             if (tracing) tr[2] = mg_globaltimer();
             const int nv = B * op.nq * op.uv;
             if (tid < nv) {
@@ -913,6 +958,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                 }
             }
             if (tracing) tr[3] = mg_globaltimer(), tr[4] = (unsigned long long)wait_cyc, tr[5] = (unsigned long long)poll_cyc;
+            flush_append();  // off the critical path: this op's outputs are already stored
             if (op.type == MG_HEAD && (op.flags & MG_LAST)) {
                 // this CTA's best logit per sequence -> its slot of the pick buffer
                 if (tid < NOUT) bestv[tid] = my_best, besti[tid] = my_besti;
@@ -932,6 +978,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
             }
         }
         if (ctl.dead) break;
+        flush_append();
 
         // ---- greedy pick (top_k = 1 of src/wasm_api.rs:120-156): best over all CTAs, lowest index on ties ----
         mg_fetch<8>(p.buf_pick, p.n_pick_ctas * B * 2, tagbase + (uint32_t)p.L + 1u, pickbuf, ctl);
@@ -1044,7 +1091,7 @@ static size_t mg_smem_bytes(const rg_gpt* m, int B, int NQ, int nslot, int max_o
     const int NOUT = B * NQ * VEC;
     size_t s = (size_t)nslot * MG_SLOT_BYTES + 128 + (size_t)max_ops * sizeof(mg_op) + (size_t)max_cd * sizeof(mg_cdesc);
     s += (size_t)B * m->F * 4 + (size_t)B * m->D * 4 + (size_t)B * res_cap * 4 + (size_t)MG_THREADS * VEC * 4 + 128 * 4 + 3 * 128 * 4;
-    s += 8 * (size_t)NOUT * 4 + 8 * 2 * MG_BMAX * 4 + 2 * (size_t)NOUT * 4 + MG_BMAX * 4 + 16 + (size_t)n_pick * B * 2 * 4;
+    s += 8 * (size_t)NOUT * 4 + 8 * 2 * MG_BMAX * 4 + 2 * (size_t)NOUT * 4 + MG_BMAX * 4 + 16 + 256 * 4 + (size_t)n_pick * B * 2 * 4;
     return s + 128;
 }
 
@@ -1174,17 +1221,10 @@ static void mg_pack_all(rg_gpt* m, rg_mega* g) {
         for (int i = 0; i < 4; i++)
             mg_pack_kernel<WT><<<g->G, 256, 0, s>>>((const WT*)lins[i]->W, lins[i]->ldw, lins[i]->b, lins[i]->N, gam[i], bet[i],
                                                     g->d_ops, g->d_cta_off, types[i], l, g->d_wpack);
-        float* ln = g->d_lnpack + (size_t)4 * l * m->D;
-        cudaMemcpyAsync(ln, y.ln1g, m->D * 4, cudaMemcpyDeviceToDevice, s);
-        cudaMemcpyAsync(ln + m->D, y.ln1b, m->D * 4, cudaMemcpyDeviceToDevice, s);
-        cudaMemcpyAsync(ln + 2 * m->D, y.ln2g, m->D * 4, cudaMemcpyDeviceToDevice, s);
-        cudaMemcpyAsync(ln + 3 * m->D, y.ln2b, m->D * 4, cudaMemcpyDeviceToDevice, s);
     }
     mg_pack_kernel<WT><<<g->G, 256, 0, s>>>((const WT*)m->head.W, m->head.ldw, m->head.b, m->head.N, m->lnfg, m->lnfb, g->d_ops,
                                             g->d_cta_off, MG_HEAD, m->L, g->d_wpack);
-    float* lnf = g->d_lnpack + (size_t)4 * m->L * m->D;
-    cudaMemcpyAsync(lnf, m->lnfg, m->D * 4, cudaMemcpyDeviceToDevice, s);
-    cudaMemcpyAsync(lnf + m->D, m->lnfb, m->D * 4, cudaMemcpyDeviceToDevice, s);
+
     m->ctx->launches += 4 * m->L + 1;
 }
 
@@ -1228,7 +1268,6 @@ static rg_status mg_prepare(rg_gpt* m, int B) {
     RG_TRY(mg_dalloc(g, (void**)&g->d_cds, g->cds.size() * sizeof(mg_cdesc)));
     RG_TRY(mg_dalloc(g, (void**)&g->d_cd_off, (g->G + 1) * sizeof(int)));
     RG_TRY(mg_dalloc(g, (void**)&g->d_wpack, g->wpack_bytes));
-    RG_TRY(mg_dalloc(g, (void**)&g->d_lnpack, (size_t)(4 * m->L + 2) * m->D * 4));
     RG_TRY(mg_dalloc(g, (void**)&g->d_trace, (size_t)g->G * g->max_ops * 8 * 8));
     RG_CUDA(cudaMemset(g->d_trace, 0, (size_t)g->G * g->max_ops * 8 * 8));
     RG_TRY(mg_dalloc(g, (void**)&g->d_abort, 16));
@@ -1296,7 +1335,7 @@ rg_status rg_mega_run(rg_gpt* m, int B, size_t pos0, size_t n_steps) {
     }
     mg_params prm;
     memset(&prm, 0, sizeof(prm));
-    prm.ops = g->d_ops, prm.cta_off = g->d_cta_off, prm.wpack = g->d_wpack, prm.lnpack = g->d_lnpack;
+    prm.ops = g->d_ops, prm.cta_off = g->d_cta_off, prm.wpack = g->d_wpack;
     prm.cds = g->d_cds, prm.cd_off = g->d_cd_off, prm.max_cd = g->max_cd;
     prm.trace = m->trace_on ? g->d_trace : nullptr;
     prm.wte = m->wte, prm.wpe = m->wpe, prm.ldt = m->ldt;
@@ -1353,7 +1392,8 @@ rg_status rg_mega_check(rg_gpt* m) {
 
 // Timestamps (ns, %globaltimer) of the last token step of the last run, per CTA and op:
 // [start, input ready, dot products done, outputs stored] then SM cycles spent waiting for ring slots and
-// for the input vector.  Rows of 10: cta, op index, type, layer, t0..t3, wait cycles, poll cycles.
+// for the input vector, then two more timestamps (input words all valid; chunk loop finished).
+// Rows of 12: cta, op index, type, layer, t0..t3, wait cycles, poll cycles, t_fetched, t_loop.
 rg_status rg_mega_trace(rg_gpt* m, unsigned long long* out, size_t cap_rows, size_t* n_rows) {
     rg_mega* g = m->mega;
     *n_rows = 0;
@@ -1367,9 +1407,9 @@ rg_status rg_mega_trace(rg_gpt* m, unsigned long long* out, size_t cap_rows, siz
             if (n >= cap_rows) break;
             const mg_op& op = g->ops[oi];
             const unsigned long long* t = &raw[((size_t)c * g->max_ops + (oi - g->cta_off[c])) * 8];
-            unsigned long long* o = out + n * 10;
+            unsigned long long* o = out + n * 12;
             o[0] = c, o[1] = oi - g->cta_off[c], o[2] = op.type, o[3] = op.layer;
-            o[4] = t[0], o[5] = t[1], o[6] = t[2], o[7] = t[3], o[8] = t[4], o[9] = t[5];
+            o[4] = t[0], o[5] = t[1], o[6] = t[2], o[7] = t[3], o[8] = t[4], o[9] = t[5], o[10] = t[6], o[11] = t[7];
             n++;
         }
     *n_rows = n;

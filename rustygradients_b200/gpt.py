@@ -157,8 +157,9 @@ class GPTModel:
         check(self._lib.rg_gpt_trace_enable(self._h, 1 if on else 0))
 
     def read_trace(self, cap_rows: int = 1 << 16) -> np.ndarray:
-        """Rows [cta, op, stage, layer, t_start, t_input, t_dots, t_stored (ns), chunk-wait cycles, poll cycles]."""
-        out = np.zeros((cap_rows, 10), dtype=np.uint64)
+        """Rows [cta, op, stage, layer, t_start, t_input, t_dots, t_stored (ns), chunk-wait cycles, poll cycles,
+        t_fetched, t_loop (ns)]."""
+        out = np.zeros((cap_rows, 12), dtype=np.uint64)
         n = C.c_size_t(0)
         check(self._lib.rg_gpt_trace_read(self._h, out.ctypes.data_as(C.POINTER(C.c_uint64)), cap_rows, C.byref(n)))
         return out[: n.value]

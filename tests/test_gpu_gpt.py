@@ -275,4 +275,4 @@ def test_persistent_kernel_equals_graph_step(backend, monkeypatch):
         backend.synchronize()
         assert backend.launch_count - l0 <= 3                    # one launch for 30 token steps
         tr_rows = a.read_trace()
-        assert tr_rows.shape[1] == 10
+        assert tr_rows.shape[1] == 12
