@@ -367,6 +367,44 @@ __device__ __noinline__ void mg_fetch(const mg_word* src, int n, uint32_t tag, f
     }
 }
 
+// Fetch of a stage input where every thread takes exactly the elements it will use itself: element k
+// belongs to thread k mod 256, the same thread that owns weight row k in the dot products.  Nothing else
+// reads dst[k], so no barrier is needed between this fetch and the dot products, and a thread starts its
+// multiply-adds as soon as ITS words have arrived.  8-byte loads, up to U in flight per thread.
+template <int U = 8>
+__device__ __noinline__ void mg_fetch_own(const mg_word* src, int n, uint32_t tag, float* dst, mg_ctl& ctl) {
+    for (int base = threadIdx.x; base < n; base += MG_THREADS * U) {
+        uint32_t pending = 0;
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (base + u * MG_THREADS < n) pending |= 1u << u;
+        uint32_t spins = 0;
+        while (pending != 0) {
+            mg_word w[U];
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                if (pending & (1u << u)) w[u] = mg_ld_word(src + base + u * MG_THREADS);
+            uint32_t done = 0;
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                if ((pending & (1u << u)) && (uint32_t)(w[u] >> 32) == tag) {
+                    dst[base + u * MG_THREADS] = __uint_as_float((uint32_t)w[u]);
+                    done |= 1u << u;
+                }
+            }
+            pending &= ~done;
+            if (pending != 0) {
+                if (++spins > MG_SPIN_LIMIT || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
+                    mg_give_up(ctl);
+                    break;
+                }
+                if (ctl.poll_sleep) __nanosleep(ctl.poll_sleep);
+            }
+        }
+        if (ctl.dead) break;
+    }
+}
+
 __device__ __forceinline__ float mg_block_max(float v, float* scratch) {
     v = rg_warp_max(v);
     mg_csync();
@@ -522,10 +560,10 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
     sp += 128 * 4;
     float* sqkv = reinterpret_cast<float*>(sp);  // q, k, v of the new row: 3 * 128
     sp += 3 * 128 * 4;
-    float* red = reinterpret_cast<float*>(sp);  // [8][NOUT]
-    sp += NWARP * NOUT * 4;
-    float* scratch = reinterpret_cast<float*>(sp);  // [8][2][B] LayerNorm partial sums
-    sp += NWARP * 2 * MG_BMAX * 4;
+    float* red2 = reinterpret_cast<float*>(sp);  // [2][8][NOUT]: alternates per projection op (see below)
+    sp += 2 * NWARP * NOUT * 4;
+    float* scratch2 = reinterpret_cast<float*>(sp);  // [2][8][B][4] per-warp LayerNorm sums (count, s1, s2, shift)
+    sp += 2 * NWARP * 4 * MG_BMAX * 4;
     float* bestv = reinterpret_cast<float*>(sp);  // [NOUT]
     sp += NOUT * 4;
     int* besti = reinterpret_cast<int*>(sp);  // [NOUT]
@@ -637,6 +675,10 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
             if (ctl.dead) break;
             prev_type = op.type;
             if (tid == 0) *reinterpret_cast<volatile int*>(s_flags) = t * nops + oi;  // the producer reads this
+            // The per-warp partial results alternate between two buffers: without a barrier between an op's input
+            // fetch and its dot products, a warp could otherwise overwrite partials the previous op's epilogue still reads.
+            float* red = red2 + (oi & 1) * (NWARP * NOUT);
+            float* scratch = scratch2 + (oi & 1) * (NWARP * 4 * MG_BMAX);
             const uint32_t tag = tagbase + (uint32_t)op.layer + 1u;
             const bool tracing = TRACE && p.trace != nullptr && t == p.n_steps - 1 && tid == 0;
             unsigned long long* tr = tracing ? p.trace + ((size_t)cta * p.max_ops + oi) * 8 : nullptr;
@@ -806,31 +848,32 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                 long long c0 = 0;
                 if constexpr (TRACE) c0 = clock64();
                 if (ln_stage) {
-                    // raw vector in (gamma is already folded into the packed weights); the thread's partial sums
-                    // go to scratch and are combined in the epilogue, after the barrier that follows the dot products
+                    // raw vector in (gamma is already folded into the packed weights), every thread its own elements.
+                    // Statistics: per warp, shifted sums with the warp's first element as shift; the 8 (count, s1, s2,
+                    // shift) tuples are combined exactly in the epilogue, after the barrier that follows the dot products.
 #pragma unroll
                     for (int b = 0; b < B; b++) {
+                        float* xr = xs + b * XLEN;
                         if (local) {
-                            for (int i = tid; i < n_in; i += MG_THREADS) xs[b * XLEN + i] = xemb[b * p.D + i];
+                            for (int i = tid; i < n_in; i += MG_THREADS) xr[i] = xemb[b * p.D + i];
                         } else {
-                            mg_fetch<2>(src + (size_t)b * n_in, n_in, in_tag, xs + b * XLEN, ctl);  // D values: <= 2 pairs per thread up to D = 1024
+                            mg_fetch_own<4>(src + (size_t)b * n_in, n_in, in_tag, xr, ctl);
                         }
-                    }
-                    if (tracing) tr[6] = mg_globaltimer();
-                    mg_csync();
-#pragma unroll
-                    for (int b = 0; b < B; b++) {
-                        const float* xr = xs + b * XLEN;
-                        const float c = xr[0];
-                        float s1 = 0.f, s2 = 0.f;
+                        const float c = __shfl_sync(RG_FULL_MASK, tid < n_in ? xr[tid] : 0.f, 0);  // lane 0 of a warp always owns an element when n >= 256
+                        float s0 = 0.f, s1 = 0.f, s2 = 0.f;
                         for (int i = tid; i < n_in; i += MG_THREADS) {
                             const float d = xr[i] - c;
+                            s0 += 1.f;
                             s1 += d;
                             s2 = fmaf(d, d, s2);
                         }
+                        s0 = rg_warp_sum(s0);
                         s1 = rg_warp_sum(s1);
                         s2 = rg_warp_sum(s2);
-                        if (lane == 0) scratch[(warp * 2) * B + b] = s1, scratch[(warp * 2 + 1) * B + b] = s2;
+                        if (lane == 0) {
+                            float* sc4 = scratch + (warp * B + b) * 4;
+                            sc4[0] = s0, sc4[1] = s1, sc4[2] = s2, sc4[3] = c;
+                        }
                     }
                     stats_pending = true;
                 } else if (op.type == MG_OPROJ) {
@@ -878,15 +921,13 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                                 }
                                 o = __fdividef(o, den);
                             }
-                            vec[b * p.D + k] = o;
+                            vec[b * p.D + k] = o;  // element k stays with thread k mod 256: no barrier before the dot products
                         }
                     }
-                    mg_csync();
                 } else {
 #pragma unroll
-                    for (int b = 0; b < B; b++) mg_fetch<8>(src + (size_t)b * n_in, n_in, in_tag, xs + b * XLEN, ctl);
+                    for (int b = 0; b < B; b++) mg_fetch_own<16>(src + (size_t)b * n_in, n_in, in_tag, xs + b * XLEN, ctl);
                     if (tracing) tr[6] = mg_globaltimer();
-                    mg_csync();
                 }
                 if constexpr (TRACE) poll_cyc += clock64() - c0;
             }
@@ -917,16 +958,25 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
             }
             if (mg_csync_or(ctl.dead)) ctl.dead = true;  // uniform from here on
             if (stats_pending && tid < NOUT) {
-                // shifted sums of all warps -> mean and 1/sqrt(biased variance + eps) (src/ops/norm.rs:41-52)
+                // combine the per-warp shifted sums exactly (common shift C = the first warp's):
+                //   sum(x - C) = s1 + n (c - C),  sum((x - C)^2) = s2 + 2 (c - C) s1 + n (c - C)^2
+                // then mean = C + S1/N and the biased variance S2/N - (S1/N)^2, eps inside the sqrt (src/ops/norm.rs:41-52)
 #pragma unroll
                 for (int b = 0; b < B; b++) {
-                    float t1s = 0.f, t2s = 0.f;
+                    const float C = scratch[(0 * B + b) * 4 + 3];
+                    float S0 = 0.f, S1 = 0.f, S2 = 0.f;
 #pragma unroll
-                    for (int w2 = 0; w2 < NWARP; w2++) t1s += scratch[(w2 * 2) * B + b], t2s += scratch[(w2 * 2 + 1) * B + b];
-                    const float rn = 1.f / (float)p.D;
-                    const float m1 = t1s * rn;
-                    mu[b] = xs[b * XLEN] + m1;
-                    rstd[b] = rsqrtf(fmaxf(fmaf(-m1, m1, t2s * rn), 0.f) + 1e-5f);
+                    for (int w2 = 0; w2 < NWARP; w2++) {
+                        const float* sc4 = scratch + (w2 * B + b) * 4;
+                        const float dc = sc4[3] - C;
+                        S0 += sc4[0];
+                        S1 += fmaf(sc4[0], dc, sc4[1]);
+                        S2 += fmaf(sc4[0] * dc, dc, fmaf(2.f * dc, sc4[1], sc4[2]));
+                    }
+                    const float rn = 1.f / S0;
+                    const float m1 = S1 * rn;
+                    mu[b] = C + m1;
+                    rstd[b] = rsqrtf(fmaxf(fmaf(-m1, m1, S2 * rn), 0.f) + 1e-5f);
                 }
             }
             stats_pending = false;
@@ -1091,7 +1141,7 @@ static size_t mg_smem_bytes(const rg_gpt* m, int B, int NQ, int nslot, int max_o
     const int NOUT = B * NQ * VEC;
     size_t s = (size_t)nslot * MG_SLOT_BYTES + 128 + (size_t)max_ops * sizeof(mg_op) + (size_t)max_cd * sizeof(mg_cdesc);
     s += (size_t)B * m->F * 4 + (size_t)B * m->D * 4 + (size_t)B * res_cap * 4 + (size_t)MG_THREADS * VEC * 4 + 128 * 4 + 3 * 128 * 4;
-    s += 8 * (size_t)NOUT * 4 + 8 * 2 * MG_BMAX * 4 + 2 * (size_t)NOUT * 4 + MG_BMAX * 4 + 16 + 256 * 4 + (size_t)n_pick * B * 2 * 4;
+    s += 2 * 8 * (size_t)NOUT * 4 + 2 * 8 * 4 * MG_BMAX * 4 + 2 * (size_t)NOUT * 4 + MG_BMAX * 4 + 16 + 256 * 4 + (size_t)n_pick * B * 2 * 4;
     return s + 128;
 }
 
@@ -1124,12 +1174,16 @@ static void mg_build_program(rg_gpt* m, rg_mega* g, int B) {
                 memset(&op, 0, sizeof(op));
                 op.type = type, op.layer = layer, op.K = K;
                 op.nq = std::min(nq, NQU), op.q0 = q, op.uv = UV;
-                const size_t budget = MG_SLOT_BYTES - 256;  // room for the trailer of the last chunk
-                const size_t bytes = (size_t)op.nq * K * ub;
-                const int nch = (int)((bytes + budget - 1) / budget);
-                int kc = rg_cdiv(K, nch);
-                kc = (kc + 31) / 32 * 32;
-                while ((size_t)op.nq * kc * ub > budget) kc -= 32;
+                // rows per chunk: a multiple of 256 so that row k of every chunk is handled by thread k mod 256
+                // (the thread that fetched input element k); a single chunk when K is small.  Only the last
+                // chunk carries the trailer (256 bytes set aside).
+                int kc = K;
+                if (K > 256) {
+                    kc = std::max(256, (int)(MG_SLOT_BYTES / ((size_t)op.nq * ub)) / 256 * 256);
+                    kc = std::min(kc, (K + 255) / 256 * 256);
+                    auto last_rows = [&](int c) { return K % c == 0 ? c : K % c; };
+                    while (kc > 256 && (size_t)op.nq * last_rows(kc) * ub + 256 > MG_SLOT_BYTES) kc -= 256;
+                }
                 op.kc = std::max(kc, 1);
                 op.nchunks = rg_cdiv(K, op.kc);
                 op.flags = first ? MG_FIRST : 0;
