@@ -37,7 +37,9 @@ typedef enum rg_status {
     RG_ERR_BACKEND = 4,       /* BackendError (CUDA / NCCL failure)    */
     RG_ERR_UNSUPPORTED = 5,   /* where the reference has unimplemented!() (src/backend/cuda.rs:436-494) */
     RG_ERR_CONTEXT_FULL = 6,  /* decode past block_size (the reference slides its window, src/wasm_api.rs:103) */
-    RG_ERR_TIMEOUT = 7        /* a bounded device-side wait gave up    */
+    RG_ERR_TIMEOUT = 7,       /* a bounded device-side wait gave up    */
+    RG_ERR_SERIALIZATION = 8, /* SerializationError (malformed file, dtype other than F32) */
+    RG_ERR_IO = 9             /* IoError (missing file, missing required weight: src/models/hf_loader.rs:233-238) */
 } rg_status;
 
 /* Message of the last failing call on this thread (maps to the String payload
@@ -210,6 +212,52 @@ RG_API rg_status rg_gpt_trace_read(rg_gpt* m, uint64_t* out, size_t cap_rows, si
  * cudaMalloc / cudaFree or any allocating library routine. */
 RG_API rg_status rg_linear_row_noalloc(const float* x, const float* W, const float* bias, float* y, size_t K,
                                        size_t N, void* stream);
+
+/* ---- weight ingest from disk (the step before the path) -------------------- */
+/* Names under which a safetensors file holds the model's tensors. */
+typedef enum rg_names {
+    RG_NAMES_AUTO = 0,   /* Hugging Face names if `wte.weight` is present, else the crate's */
+    RG_NAMES_RUSTY = 1,  /* token_embedding.weight, position_embedding.weight, layer_{l}.attn.{q,k,v,out_proj}.weight
+                          * (or the fused layer_{l}.attn.qkv.weight [D,3D] + attn.proj.weight), layer_{l}.ffn.fc{1,2}.weight,
+                          * layer_{l}.ln{1,2}.{gamma,beta}, output_projection.weight: examples/serialization_demo.rs:24-101,
+                          * examples/train_gpt_e2e.rs:146-160.  Optional: `.bias` of every projection (0 when absent),
+                          * ln_f.{gamma,beta} (1 / 0 when absent) */
+    RG_NAMES_HF_GPT2 = 2 /* wte, wpe, h.{l}.attn.c_attn / c_proj, h.{l}.ln_1 / ln_2, h.{l}.mlp.c_fc / c_proj, ln_f, with or
+                          * without the `transformer.` prefix: src/models/hf_loader.rs:256-276.  c_attn [D,3D] is split into
+                          * q | k | v; the LM head is lm_head.weight or the token table, transposed, with a zero bias */
+} rg_names;
+
+/* ModelMetadata {model_type, vocab_size, embedding_dim, num_layers, num_heads, block_size, dropout}
+ * (src/serialization/mod.rs:28-37) from the sidecar `<weights>.safetensors.json` that save_model writes
+ * (src/serialization/safetensors_format.rs:76-81) or from the "metadata" object of a JsonCheckpoint
+ * (src/serialization/mod.rs:68-74).  Sets the five GptConfig fields of *cfg and leaves the others alone. */
+RG_API rg_status rg_model_metadata_read(const char* path, rg_gpt_config* cfg);
+/* load_model (src/serialization/safetensors_format.rs:89-138) + the copy into the model the reference never
+ * finished (src/models/hf_loader.rs:290-296).  F32 tensors only (RG_ERR_SERIALIZATION otherwise, as :111-116);
+ * a missing required tensor is RG_ERR_IO, a wrong shape RG_ERR_SHAPE.  `names` is an rg_names value. */
+RG_API rg_status rg_gpt_load_safetensors(rg_gpt* m, const char* path, int names);
+/* WasmGptTrainer::loadWeightsFromJson (src/wasm_api.rs:179-199): a JSON array of {shape, data} in parameters()
+ * order, or a JsonCheckpoint {metadata, weights, step, loss} (src/serialization/mod.rs:52-74, :104-113). */
+RG_API rg_status rg_gpt_load_json(rg_gpt* m, const char* path);
+
+/* ---- tokenizers (text in / text out around the path; host code) ------------ */
+typedef struct rg_tokenizer rg_tokenizer;
+/* CharTokenizer::new(text): ids = rank among the sorted distinct characters (src/tokenization/char_tokenizer.rs:34-60) */
+RG_API rg_status rg_tokenizer_char_from_text(const char* text_utf8, size_t len, rg_tokenizer** out);
+/* CharTokenizer::from_vocab(&[char]): Unicode scalar values in id order (src/tokenization/char_tokenizer.rs:63-84) */
+RG_API rg_status rg_tokenizer_char_from_vocab(const uint32_t* codepoints, size_t n, rg_tokenizer** out);
+/* BPETokenizer::load (src/tokenization/bpe_tokenizer.rs:224-247): {token_to_id, id_to_token, merges, vocab_size} */
+RG_API rg_status rg_tokenizer_bpe_load(const char* path, rg_tokenizer** out);
+/* Tokenizer::vocab_size (src/tokenization/mod.rs) */
+RG_API rg_status rg_tokenizer_vocab_size(const rg_tokenizer* t, size_t* out);
+/* Tokenizer::encode (char_tokenizer.rs:95-100, bpe_tokenizer.rs:250-267).  *n_out receives the number of ids;
+ * ids_out may be NULL to ask for it only; a too small `cap` or text that is not UTF-8 is RG_ERR_INVALID_INPUT. */
+RG_API rg_status rg_tokenizer_encode(const rg_tokenizer* t, const char* text_utf8, size_t len, uint32_t* ids_out, size_t cap,
+                                     size_t* n_out);
+/* Tokenizer::decode (char_tokenizer.rs:102-107, bpe_tokenizer.rs:269-275); unknown ids are skipped.  UTF-8, not
+ * NUL-terminated; *len_out receives the byte length; out may be NULL to ask for it only. */
+RG_API rg_status rg_tokenizer_decode(const rg_tokenizer* t, const uint32_t* ids, size_t n, char* out, size_t cap, size_t* len_out);
+RG_API void rg_tokenizer_free(rg_tokenizer* t);
 
 #ifdef __cplusplus
 }

@@ -32,6 +32,8 @@ struct BackendError : Error { using Error::Error; };
 struct Unsupported : Error { using Error::Error; };
 struct ContextFull : Error { using Error::Error; };
 struct DeviceTimeout : Error { using Error::Error; };
+struct SerializationError : Error { using Error::Error; };
+struct IoError : Error { using Error::Error; };
 
 inline void check(rg_status s) {
     if (s == RG_OK) return;
@@ -44,6 +46,8 @@ inline void check(rg_status s) {
         case RG_ERR_UNSUPPORTED: throw Unsupported(s, msg);
         case RG_ERR_CONTEXT_FULL: throw ContextFull(s, msg);
         case RG_ERR_TIMEOUT: throw DeviceTimeout(s, msg);
+        case RG_ERR_SERIALIZATION: throw SerializationError(s, msg);
+        case RG_ERR_IO: throw IoError(s, msg);
         default: throw Error(s, msg);
     }
 }
@@ -176,6 +180,12 @@ class GPTModel {
         for (auto& s : shapes) sp.push_back(s.data());
         check(rg_gpt_load_params(m_.get(), data.data(), sp.data(), nd.data(), (int)tensors.size()));
     }
+    // load_model (src/serialization/safetensors_format.rs:89-138) + the copy into the model
+    void load_safetensors(const std::string& path, rg_names names = RG_NAMES_AUTO) {
+        check(rg_gpt_load_safetensors(m_.get(), path.c_str(), (int)names));
+    }
+    // loadWeightsFromJson (src/wasm_api.rs:179-199) from a file, or a JsonCheckpoint (src/serialization/mod.rs:52-74)
+    void load_json(const std::string& path) { check(rg_gpt_load_json(m_.get(), path.c_str())); }
     // Module::forward: idx [B,T] carried as f32 -> logits [B,T,V]
     std::vector<float> forward(const std::vector<float>& idx, size_t B, size_t T) {
         std::vector<float> out(B * T * cfg_.vocab_size);
@@ -195,6 +205,52 @@ class GPTModel {
     B200Backend be_;
     GptConfig cfg_;
     std::shared_ptr<rg_gpt> m_;
+};
+
+// trait Tokenizer (src/tokenization/mod.rs): encode / decode / vocab_size
+class Tokenizer {
+  public:
+    // CharTokenizer::new(text)
+    static Tokenizer chars_of(const std::string& text) {
+        rg_tokenizer* t = nullptr;
+        check(rg_tokenizer_char_from_text(text.data(), text.size(), &t));
+        return Tokenizer(t);
+    }
+    // CharTokenizer::from_vocab(&[char])
+    static Tokenizer char_vocab(const std::vector<uint32_t>& codepoints) {
+        rg_tokenizer* t = nullptr;
+        check(rg_tokenizer_char_from_vocab(codepoints.data(), codepoints.size(), &t));
+        return Tokenizer(t);
+    }
+    // BPETokenizer::load(path)
+    static Tokenizer bpe_load(const std::string& path) {
+        rg_tokenizer* t = nullptr;
+        check(rg_tokenizer_bpe_load(path.c_str(), &t));
+        return Tokenizer(t);
+    }
+    std::vector<uint32_t> encode(const std::string& text) const {
+        size_t n = 0;
+        check(rg_tokenizer_encode(t_.get(), text.data(), text.size(), nullptr, 0, &n));
+        std::vector<uint32_t> ids(n);
+        check(rg_tokenizer_encode(t_.get(), text.data(), text.size(), ids.data(), ids.size(), &n));
+        return ids;
+    }
+    std::string decode(const std::vector<uint32_t>& ids) const {
+        size_t n = 0;
+        check(rg_tokenizer_decode(t_.get(), ids.data(), ids.size(), nullptr, 0, &n));
+        std::string s(n, '\0');
+        check(rg_tokenizer_decode(t_.get(), ids.data(), ids.size(), &s[0], s.size(), &n));
+        return s;
+    }
+    size_t vocab_size() const {
+        size_t n = 0;
+        check(rg_tokenizer_vocab_size(t_.get(), &n));
+        return n;
+    }
+
+  private:
+    explicit Tokenizer(rg_tokenizer* t) : t_(t, [](rg_tokenizer* p) { rg_tokenizer_free(p); }) {}
+    std::shared_ptr<rg_tokenizer> t_;
 };
 
 }  // namespace rg

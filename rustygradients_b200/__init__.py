@@ -3,10 +3,12 @@
 The arithmetic lives in lib/librg_b200.so (CUDA, sm_100a, C ABI in
 include/rg_b200.h); this package is the thin host-side mirror of the reference's
 `Backend` trait, `GptConfig`, `GPTModel` and `generate`."""
-from ._lib import (BackendError, ContextFull, DeviceTimeout, DimensionError, InvalidInput,
-                   RustyGradientsError, ShapeError, Unsupported)
+from ._lib import (BackendError, ContextFull, DeviceTimeout, DimensionError, InvalidInput, IoError,
+                   RustyGradientsError, SerializationError, ShapeError, Unsupported)
 from .backend import B200Backend, Storage
 from .gpt import GptConfig, GPTModel
+from .tokenization import BPETokenizer, CharTokenizer
 
 __all__ = ["B200Backend", "Storage", "GptConfig", "GPTModel", "RustyGradientsError", "ShapeError",
-           "DimensionError", "InvalidInput", "BackendError", "Unsupported", "ContextFull", "DeviceTimeout"]
+           "DimensionError", "InvalidInput", "BackendError", "Unsupported", "ContextFull", "DeviceTimeout",
+           "SerializationError", "IoError", "CharTokenizer", "BPETokenizer"]

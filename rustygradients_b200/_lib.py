@@ -12,7 +12,8 @@ LIB_PATH = os.path.join(HERE, "lib", "librg_b200.so")
 
 # rg_status values (include/rg_b200.h)
 RG_OK, RG_ERR_SHAPE, RG_ERR_DIMENSION, RG_ERR_INVALID_INPUT, RG_ERR_BACKEND, \
-    RG_ERR_UNSUPPORTED, RG_ERR_CONTEXT_FULL, RG_ERR_TIMEOUT = range(8)
+    RG_ERR_UNSUPPORTED, RG_ERR_CONTEXT_FULL, RG_ERR_TIMEOUT, RG_ERR_SERIALIZATION, RG_ERR_IO = range(10)
+RG_NAMES_AUTO, RG_NAMES_RUSTY, RG_NAMES_HF_GPT2 = 0, 1, 2
 RG_ACT_RELU, RG_ACT_GELU_TANH = 0, 1
 RG_DTYPE_F32, RG_DTYPE_BF16 = 0, 1
 
@@ -50,8 +51,16 @@ class DeviceTimeout(RustyGradientsError):
     status = RG_ERR_TIMEOUT
 
 
+class SerializationError(RustyGradientsError):
+    status = RG_ERR_SERIALIZATION
+
+
+class IoError(RustyGradientsError):
+    status = RG_ERR_IO
+
+
 _ERRORS = {c.status: c for c in (ShapeError, DimensionError, InvalidInput, BackendError,
-                                 Unsupported, ContextFull, DeviceTimeout)}
+                                 Unsupported, ContextFull, DeviceTimeout, SerializationError, IoError)}
 
 
 class GptConfigC(C.Structure):
@@ -123,6 +132,16 @@ SIGNATURES = {
     "rg_gpt_trace_enable": (None, [_P, C.c_int]),
     "rg_gpt_trace_read": (None, [_P, C.POINTER(C.c_uint64), _SZ, _SZP]),
     "rg_linear_row_noalloc": (None, [_P, _P, _P, _P, _SZ, _SZ, _P]),
+    "rg_model_metadata_read": (None, [C.c_char_p, C.POINTER(GptConfigC)]),
+    "rg_gpt_load_safetensors": (None, [_P, C.c_char_p, C.c_int]),
+    "rg_gpt_load_json": (None, [_P, C.c_char_p]),
+    "rg_tokenizer_char_from_text": (None, [C.c_char_p, _SZ, _PP]),
+    "rg_tokenizer_char_from_vocab": (None, [_U32P, _SZ, _PP]),
+    "rg_tokenizer_bpe_load": (None, [C.c_char_p, _PP]),
+    "rg_tokenizer_vocab_size": (None, [_P, _SZP]),
+    "rg_tokenizer_encode": (None, [_P, C.c_char_p, _SZ, _U32P, _SZ, _SZP]),
+    "rg_tokenizer_decode": (None, [_P, _U32P, _SZ, C.c_char_p, _SZ, _SZP]),
+    "rg_tokenizer_free": (C.c_int, [_P]),
 }
 
 _lib = None

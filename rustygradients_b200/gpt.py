@@ -88,6 +88,16 @@ class GPTModel:
         ndims = (C.c_int * n)(*[a.ndim for a in arrs])
         check(self._lib.rg_gpt_load_params(self._h, data, shapes, ndims, n))
 
+    def load_safetensors(self, path: str, names: str = "auto") -> None:
+        """`load_model` (src/serialization/safetensors_format.rs:89-138) followed by the copy into the model;
+        names: "auto", "rusty" (the crate's descriptive names) or "hf_gpt2" (src/models/hf_loader.rs:256-276)."""
+        code = {"auto": _lib.RG_NAMES_AUTO, "rusty": _lib.RG_NAMES_RUSTY, "hf_gpt2": _lib.RG_NAMES_HF_GPT2}[names]
+        check(self._lib.rg_gpt_load_safetensors(self._h, path.encode(), code))
+
+    def load_json(self, path: str) -> None:
+        """`loadWeightsFromJson` (src/wasm_api.rs:179-199) / `load_json` (src/serialization/mod.rs:104-113)."""
+        check(self._lib.rg_gpt_load_json(self._h, path.encode()))
+
     # -- Module::forward (gpt.rs:58-83)
     def forward(self, idx: np.ndarray) -> np.ndarray:
         idx = np.ascontiguousarray(idx, dtype=np.float32)

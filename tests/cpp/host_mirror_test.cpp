@@ -78,6 +78,27 @@ int main() {
         threw = true;
     }
     EXPECT(threw);
+    // Tokenizer trait: the reference's own char-tokenizer checks (src/tokenization/char_tokenizer.rs:113-161)
+    auto tok = rg::Tokenizer::chars_of("Hello, world!");
+    auto enc = tok.encode("Hello");
+    EXPECT(enc.size() == 5 && tok.decode(enc) == "Hello");
+    EXPECT(rg::Tokenizer::chars_of("aabbcc").vocab_size() == 3);
+    auto abc = rg::Tokenizer::char_vocab({'a', 'b', 'c'});
+    EXPECT(abc.encode("cab") == (std::vector<uint32_t>{2, 0, 1}));
+    threw = false;
+    try {
+        rg::Tokenizer::bpe_load("/nonexistent/tokenizer.json");
+    } catch (const rg::IoError&) {
+        threw = true;
+    }
+    EXPECT(threw);
+    threw = false;
+    try {
+        model.load_safetensors("/nonexistent/model.safetensors");
+    } catch (const rg::IoError&) {
+        threw = true;
+    }
+    EXPECT(threw);
     std::printf("OK\n");
     return 0;
 }
