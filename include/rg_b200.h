@@ -186,6 +186,10 @@ RG_API double rg_gpt_decode_step_bytes(const rg_gpt* m, size_t B, double mean_ct
  * all-reduces of [B, embedding_dim] over NVLink, the head one all-gather of logits. */
 RG_API rg_status rg_gpt_tp_unique_id(uint8_t id_out[128]);
 RG_API rg_status rg_gpt_tp_init(rg_gpt* m, const uint8_t id[128]);
+/* 1 when the token step's all-reduces run as the library's own one-shot kernel over peer-mapped memory
+ * (NVLink stores + tagged words), 0 when they go through NCCL (RG_B200_TP_ALLREDUCE=nccl, or a GPU pair
+ * without peer access).  No counterpart in the reference. */
+RG_API int rg_gpt_tp_fused(const rg_gpt* m);
 
 /* Profiling aid of the persistent token-loop kernel (engine-only, nothing to mirror in the
  * reference): when enabled, the last token step of every rg_gpt_decode_run records device

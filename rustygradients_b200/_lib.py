@@ -129,6 +129,7 @@ SIGNATURES = {
     "rg_gpt_decode_step_bytes": (C.c_double, [_P, _SZ, C.c_double]),
     "rg_gpt_tp_unique_id": (None, [C.POINTER(C.c_uint8)]),
     "rg_gpt_tp_init": (None, [_P, C.POINTER(C.c_uint8)]),
+    "rg_gpt_tp_fused": (C.c_int, [_P]),
     "rg_gpt_trace_enable": (None, [_P, C.c_int]),
     "rg_gpt_trace_read": (None, [_P, C.POINTER(C.c_uint64), _SZ, _SZP]),
     "rg_linear_row_noalloc": (None, [_P, _P, _P, _P, _SZ, _SZ, _P]),

@@ -64,6 +64,71 @@ static __global__ void rg_reduce_parts_kernel(const float* __restrict__ parts, i
     if (ld_out) out[(i / n_bias) * ld_out + i % n_bias] = v;
     else out[i] = v;
 }
+static void tp_peer_close(rg_gpt* m);
+static rg_status tp_check(rg_gpt* m);
+// ---- token-step all-reduce over peer memory (tensor parallel) ---------------------------------------------
+// One kernel = local reduction of the projection's k-split partial sums + all-reduce over the ranks.  Every
+// rank stores its value of element i, together with a tag, as ONE 64-bit word into slot [parity][rank][i] of
+// every rank's receive buffer (plain stores through NVLink to peer-mapped memory), then polls the tp_size
+// words of element i in its own buffer until their tags match and adds them in rank order, so every rank
+// obtains bit-identical sums.  Data and flag travel in the same word: no separate signal, no barrier.
+// Two parities alternate between consecutive all-reduces: a rank can be at most one all-reduce ahead of a
+// peer that is still reading, because the next one needs that peer's contribution.
+// Every wait is bounded: after RG_TP_SPIN_LIMIT polls the thread sets *err and gives up.
+#define RG_TP_MAX 16
+#define RG_TP_SPIN_LIMIT (1u << 22)
+struct rg_tp_ar_args {
+    const float* parts;  // [nparts][cnt]
+    int nparts;
+    size_t cnt;
+    float* out;  // [cnt]
+    unsigned long long* peer[RG_TP_MAX];
+    int T, rank;
+    size_t slot;  // words per (parity, rank)
+    const unsigned* epoch;
+    int site, nsites;
+    int* err;
+};
+static __global__ void __launch_bounds__(256) rg_tp_allreduce_kernel(rg_tp_ar_args a) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.cnt) return;
+    const unsigned seq = *a.epoch * (unsigned)a.nsites + (unsigned)a.site;
+    const unsigned tag = seq + 1u;
+    const size_t par = seq & 1u;
+    float v = 0.f;
+    for (int z = 0; z < a.nparts; z++) v += a.parts[(size_t)z * a.cnt + i];
+    const unsigned long long word = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+    const size_t mine = (par * a.T + a.rank) * a.slot + i;
+    for (int r = 0; r < a.T; r++)
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(a.peer[r] + mine), "l"(word) : "memory");
+    const unsigned long long* own = a.peer[a.rank] + par * a.T * a.slot + i;
+    float vals[RG_TP_MAX];
+    unsigned pending = (1u << a.T) - 1u, spins = 0;
+    while (pending) {
+        unsigned long long w[RG_TP_MAX];
+#pragma unroll
+        for (int r = 0; r < RG_TP_MAX; r++)
+            if (r < a.T && (pending & (1u << r)))
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w[r]) : "l"(own + (size_t)r * a.slot) : "memory");
+#pragma unroll
+        for (int r = 0; r < RG_TP_MAX; r++)
+            if (r < a.T && (pending & (1u << r)) && (unsigned)(w[r] >> 32) == tag) {
+                vals[r] = __uint_as_float((unsigned)w[r]);
+                pending &= ~(1u << r);
+            }
+        if (pending && (++spins > RG_TP_SPIN_LIMIT || ((spins & 1023u) == 0 && *(volatile int*)a.err))) {
+            *a.err = 1;
+            break;
+        }
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int r = 0; r < RG_TP_MAX; r++)
+        if (r < a.T) sum += (pending & (1u << r)) ? 0.f : vals[r];
+    a.out[i] = sum;
+}
+static __global__ void rg_bump_kernel(unsigned* p) { *p += 1u; }
+
 // x[m][n] += t[m][n] + bias[n]
 static __global__ void rg_add_bias_res_kernel(float* __restrict__ x, const float* __restrict__ t,
                                               const float* __restrict__ bias, size_t rows, int N) {
@@ -293,6 +358,7 @@ extern "C" rg_status rg_gpt_destroy(rg_gpt* m) {
     cudaSetDevice(m->ctx->device);
     cudaStreamSynchronize(m->ctx->stream);
     if (m->graph) cudaGraphExecDestroy(m->graph);
+    tp_peer_close(m);
     if (m->nccl_comm && g_nccl.ok) g_nccl.CommDestroy((ncclComm_t)m->nccl_comm);
     rg_mega_destroy(m);
     for (void* p : m->allocs) cudaFree(p);
@@ -732,14 +798,25 @@ static void launch_attn_step(rg_gpt* m, int l, int B) {
 // Enqueue the kernels of one token step for B sequences; returns how many.
 // Tensor parallel: the k-split partials of a row-split projection are summed locally, then over the ranks;
 // returns the "producer" the next stage reads (one part: the reduced vector).
-static rg_linear tp_reduce(rg_gpt* m, const rg_linear& lin, int B, int* n) {
+static rg_linear tp_reduce(rg_gpt* m, const rg_linear& lin, int B, int* n, int site) {
     rg_linear r = lin;
     if (m->tp_size == 1) return r;
     const size_t cnt = (size_t)B * lin.N;
-    rg_reduce_parts_kernel<<<rg_cdiv((long long)cnt, 256), 256, 0, m->ctx->stream>>>(lin.parts, lin.ksplit, cnt, nullptr, 1,
-                                                                                   m->tp_vec);
-    g_nccl.AllReduce(m->tp_vec, m->tp_vec, cnt, ncclFloat32, ncclSum, (ncclComm_t)m->nccl_comm, m->ctx->stream);
-    *n += 2;
+    if (m->tp_fused) {
+        rg_tp_ar_args a;
+        memset(&a, 0, sizeof(a));
+        a.parts = lin.parts, a.nparts = lin.ksplit, a.cnt = cnt, a.out = m->tp_vec;
+        for (int p = 0; p < m->tp_size; p++) a.peer[p] = m->tp_peer[p];
+        a.T = m->tp_size, a.rank = m->tp_rank, a.slot = (size_t)m->Bmax * m->D;
+        a.epoch = m->d_tp_epoch, a.site = site, a.nsites = 2 * m->L, a.err = m->d_tp_err;
+        rg_tp_allreduce_kernel<<<rg_cdiv((long long)cnt, 256), 256, 0, m->ctx->stream>>>(a);
+        *n += 1;
+    } else {
+        rg_reduce_parts_kernel<<<rg_cdiv((long long)cnt, 256), 256, 0, m->ctx->stream>>>(lin.parts, lin.ksplit, cnt, nullptr, 1,
+                                                                                       m->tp_vec);
+        g_nccl.AllReduce(m->tp_vec, m->tp_vec, cnt, ncclFloat32, ncclSum, (ncclComm_t)m->nccl_comm, m->ctx->stream);
+        *n += 2;
+    }
     r.parts = m->tp_vec, r.ksplit = 1;
     return r;
 }
@@ -748,6 +825,10 @@ static rg_linear tp_reduce(rg_gpt* m, const rg_linear& lin, int B, int* n) {
 static int enqueue_step(rg_gpt* m, int B) {
     cudaStream_t s = m->ctx->stream;
     int n = 0;
+    if (m->tp_fused) {
+        rg_bump_kernel<<<1, 1, 0, s>>>(m->d_tp_epoch);  // every rank runs the same steps: the tags agree
+        n++;
+    }
     if (m->bf16)
         rg_embed_step_kernel<__nv_bfloat16><<<B, 128, 0, s>>>(m->tokens, m->C, (const __nv_bfloat16*)m->wte,
                                                               (const __nv_bfloat16*)m->wpe, m->D, m->ldt, m->xa,
@@ -773,7 +854,7 @@ static int enqueue_step(rg_gpt* m, int B) {
         memset(&ia, 0, sizeof(ia));
         ia.kind = RG_IN_ATTN, ia.ap = m->ap, ia.H = m->Hl, ia.hd = m->hd, ia.NS = m->NS, ia.post = RG_POST_NONE;
         launch_gemv(m, y.o, ia, B);
-        const rg_linear o_red = tp_reduce(m, y.o, B, &n);
+        const rg_linear o_red = tp_reduce(m, y.o, B, &n, 2 * l);
         // x = x + bo + partials; LN2; FC1 (this rank's hidden columns)
         rg_vec_in i1 = vec_reduce(m->xb, y.o.b, &o_red, RG_POST_LN);
         i1.gamma = y.ln2g, i1.beta = y.ln2b, i1.store = m->xa;
@@ -781,7 +862,7 @@ static int enqueue_step(rg_gpt* m, int B) {
         // act(b1 + partials); FC2 (row-split)
         rg_vec_in i2 = vec_reduce(nullptr, y.fc1.b, &y.fc1, act_post);
         launch_gemv(m, y.fc2, i2, B);
-        prev_fc2 = tp_reduce(m, y.fc2, B, &n);
+        prev_fc2 = tp_reduce(m, y.fc2, B, &n, 2 * l + 1);
         prev_b2 = y.fc2.b;
         have_prev = true;
         n += 5;
@@ -945,6 +1026,7 @@ extern "C" rg_status rg_gpt_decode_step(rg_gpt* m, const uint32_t* tok, float* l
     if (logits) RG_CUDA(cudaMemcpyAsync(logits, m->logits, B * (size_t)m->V * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
     if (argmax) RG_CUDA(cudaMemcpyAsync(argmax, m->picks, B * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
     RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    RG_TRY(tp_check(m));
     return rg_mega_check(m);
 }
 
@@ -979,6 +1061,7 @@ extern "C" rg_status rg_gpt_read_tokens(rg_gpt* m, size_t from, size_t n, uint32
         RG_CUDA(cudaMemcpy2DAsync(out, n * 4, m->tokens + from, (size_t)m->C * 4, n * 4, m->curB, cudaMemcpyDeviceToHost,
                                   m->ctx->stream));
     RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    RG_TRY(tp_check(m));
     return rg_mega_check(m);
 }
 
@@ -1044,7 +1127,8 @@ extern "C" rg_status rg_gpt_generate(rg_gpt* m, const uint32_t* prompt, size_t B
                                       m->ctx->stream));
         }
         RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
-        return rg_mega_check(m);
+        RG_TRY(tp_check(m));
+    return rg_mega_check(m);
     }
     // The reference's loop proper (no mask, so no cache): every new id re-runs the
     // whole window of the last block_size ids (wasm_api.rs:102-118).
@@ -1087,6 +1171,75 @@ extern "C" rg_status rg_gpt_tp_unique_id(uint8_t id_out[128]) {
     return RG_OK;
 }
 
+static void tp_peer_close(rg_gpt* m) {
+    for (int r = 0; r < RG_TP_MAX; r++) {
+        if (m->tp_peer[r] && r != m->tp_rank) cudaIpcCloseMemHandle(m->tp_peer[r]);
+        m->tp_peer[r] = nullptr;
+    }
+    m->tp_fused = false;
+}
+
+// A wait of the peer-memory all-reduce that ran out (a rank that never arrived) -> RG_ERR_TIMEOUT; call after a sync.
+static rg_status tp_check(rg_gpt* m) {
+    if (!m->tp_fused) return RG_OK;
+    int err = 0;
+    RG_CUDA(cudaMemcpy(&err, m->d_tp_err, 4, cudaMemcpyDeviceToHost));
+    if (err) return rg_fail(RG_ERR_TIMEOUT, "tensor-parallel all-reduce: a peer's contribution did not arrive in time");
+    return RG_OK;
+}
+
+// Maps every rank's receive buffer into every other rank (CUDA IPC; one process per GPU on one node) for the
+// token step's one-shot all-reduce.  All ranks end up in the same mode: if any of them cannot map a peer
+// (no peer access between the two GPUs, IPC unavailable) or RG_B200_TP_ALLREDUCE=nccl is set, all keep NCCL.
+static rg_status tp_peer_setup(rg_gpt* m) {
+    const int T = m->tp_size;
+    cudaStream_t s = m->ctx->stream;
+    const char* mode = getenv("RG_B200_TP_ALLREDUCE");
+    int ok = (T <= RG_TP_MAX && !(mode && strcmp(mode, "nccl") == 0)) ? 1 : 0;
+    const size_t words = 2 * (size_t)T * m->Bmax * m->D;
+    RG_TRY(dalloc(m, (void**)&m->tp_recv, words * 8));
+    RG_TRY(dalloc(m, (void**)&m->d_tp_epoch, 16));
+    RG_CUDA(cudaMemsetAsync(m->tp_recv, 0, words * 8, s));  // tag 0 never matches: tags start at 1
+    RG_CUDA(cudaMemsetAsync(m->d_tp_epoch, 0, 16, s));
+    m->d_tp_err = reinterpret_cast<int*>(m->d_tp_epoch + 2);
+    // exchange the IPC handles over the communicator that exists already
+    cudaIpcMemHandle_t mine;
+    memset(&mine, 0, sizeof(mine));
+    if (cudaIpcGetMemHandle(&mine, m->tp_recv) != cudaSuccess) ok = 0, (void)cudaGetLastError();
+    char* dh = nullptr;
+    RG_TRY(dalloc(m, (void**)&dh, (size_t)(T + 1) * sizeof(mine)));
+    RG_CUDA(cudaMemcpyAsync(dh + (size_t)T * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice, s));
+    RG_NCCL(g_nccl.AllGather(dh + (size_t)T * sizeof(mine), dh, sizeof(mine), ncclInt8, (ncclComm_t)m->nccl_comm, s));
+    std::vector<cudaIpcMemHandle_t> all((size_t)T);
+    RG_CUDA(cudaMemcpyAsync(all.data(), dh, (size_t)T * sizeof(mine), cudaMemcpyDeviceToHost, s));
+    RG_CUDA(cudaStreamSynchronize(s));
+    for (int r = 0; r < T && ok; r++) {
+        if (r == m->tp_rank) {
+            m->tp_peer[r] = m->tp_recv;
+            continue;
+        }
+        void* p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, all[(size_t)r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            (void)cudaGetLastError();
+            ok = 0;
+            break;
+        }
+        m->tp_peer[r] = static_cast<unsigned long long*>(p);
+    }
+    // unanimous decision: minimum of the ranks' flags
+    float* df = reinterpret_cast<float*>(dh);
+    const float okf = (float)ok;
+    RG_CUDA(cudaMemcpyAsync(df, &okf, 4, cudaMemcpyHostToDevice, s));
+    RG_NCCL(g_nccl.AllReduce(df, df, 1, ncclFloat32, ncclMin, (ncclComm_t)m->nccl_comm, s));
+    float all_ok = 0.f;
+    RG_CUDA(cudaMemcpyAsync(&all_ok, df, 4, cudaMemcpyDeviceToHost, s));
+    RG_CUDA(cudaStreamSynchronize(s));
+    dfree(m, dh);
+    m->tp_fused = all_ok > 0.5f;
+    if (!m->tp_fused) tp_peer_close(m);
+    return RG_OK;
+}
+
 extern "C" rg_status rg_gpt_tp_init(rg_gpt* m, const uint8_t id_in[128]) {
     if (!m || !id_in) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
     if (m->tp_size <= 1) return rg_fail(RG_ERR_INVALID_INPUT, "the model was created with tp_size <= 1");
@@ -1098,8 +1251,10 @@ extern "C" rg_status rg_gpt_tp_init(rg_gpt* m, const uint8_t id_in[128]) {
     ncclComm_t comm = nullptr;
     RG_NCCL(g_nccl.CommInitRank(&comm, m->tp_size, id, m->tp_rank));
     m->nccl_comm = comm;
-    return RG_OK;
+    return tp_peer_setup(m);
 }
+
+extern "C" int rg_gpt_tp_fused(const rg_gpt* m) { return m && m->tp_fused ? 1 : 0; }
 
 extern "C" rg_status rg_gpt_trace_enable(rg_gpt* m, int on) {
     if (!m) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");

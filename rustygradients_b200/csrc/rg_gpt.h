@@ -30,6 +30,13 @@ struct rg_gpt {
     void* nccl_comm = nullptr;
     float *tp_vec = nullptr, *tp_gather = nullptr, *tp_local = nullptr;  // token-step collectives
     float *ptp = nullptr, *pgather = nullptr;                           // prompt-pass collectives
+    // one-shot all-reduce of the token step over peer memory: every rank's receive buffer
+    // [2 parities][tp_size ranks][Bmax * D] of {f32 value, 32-bit tag} words, mapped into every other rank
+    unsigned long long* tp_recv = nullptr;
+    unsigned long long* tp_peer[16] = {};
+    bool tp_fused = false;
+    unsigned* d_tp_epoch = nullptr;  // token steps enqueued so far (tags)
+    int* d_tp_err = nullptr;         // set by a wait that gave up
     size_t pgatherCap = 0;
     bool bf16 = false, loaded = false;
     size_t wsize = 4;

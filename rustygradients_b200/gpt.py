@@ -57,6 +57,10 @@ class GPTModel:
         buf = (C.c_uint8 * 128)(*unique_id)
         check(self._lib.rg_gpt_tp_init(self._h, buf))
 
+    def tp_fused(self) -> bool:
+        """True when the token step's all-reduces run as the one-shot kernel over peer memory (not NCCL)."""
+        return bool(self._lib.rg_gpt_tp_fused(self._h))
+
     def close(self) -> None:
         if self._h:
             self._lib.rg_gpt_destroy(self._h)

@@ -33,7 +33,8 @@ def test_tp_shards_cover_everything():
         assert sh[0][1] - sh[-1][1] <= 1      # 25 heads over 8 ranks: 4,3,3,3,3,3,3,3
 
 
-def _rank(rank, world, port, q):
+def _rank(rank, world, port, q, allreduce):
+    os.environ["RG_B200_TP_ALLREDUCE"] = allreduce
     import torch
     import torch.distributed as dist
     import rustygradients_b200 as rg
@@ -54,6 +55,7 @@ def _rank(rank, world, port, q):
         ident = [rg.GPTModel.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ident, src=0)
         m.tp_init(ident[0])
+        fused = m.tp_fused()
         ids = np.concatenate([prompt, toks], 1)
         logits, picks = teacher_forced(m, ids, 10)
         err = np.abs(logits - want)
@@ -62,7 +64,7 @@ def _rank(rank, world, port, q):
         ferr = float(np.abs(full - O.forward(params, cfg, ids[:, :20], causal=True, act="gelu_tanh")).max())
         out = m.generate(prompt, 12)
         results[name] = (float(err.max()), rel, ferr, bool(np.array_equal(picks, logits.argmax(-1))),
-                         out.tolist(), F32_TOL, BF16_REL_TOL)
+                         out.tolist(), F32_TOL, BF16_REL_TOL, fused)
         m.close()
     q.put((rank, results))
     dist.barrier()
@@ -70,7 +72,10 @@ def _rank(rank, world, port, q):
 
 
 @pytest.mark.gpu
-def test_tensor_parallel_two_gpus():
+@pytest.mark.parametrize("allreduce", ["peer", "nccl"])
+def test_tensor_parallel_two_gpus(allreduce):
+    """allreduce = "peer": the token step's all-reduces are the library's one-shot kernel over peer-mapped memory
+    (and must really be: tp_fused); "nccl": the same step with NCCL collectives."""
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
@@ -81,15 +86,16 @@ def test_tensor_parallel_two_gpus():
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_rank, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_rank, args=(r, 2, port, q, allreduce)) for r in range(2)]
     [p.start() for p in procs]
     res = dict(q.get(timeout=600) for _ in range(2))
     [p.join(60) for p in procs]
     for name in ("f32", "bf16"):
         a, b = res[0][name], res[1][name]
         assert a[4] == b[4]                                   # both ranks generate the same ids
-        for maxabs, rel, ferr, picks_ok, _, f32_tol, bf16_tol in (a, b):
+        for maxabs, rel, ferr, picks_ok, _, f32_tol, bf16_tol, fused in (a, b):
             assert picks_ok
+            assert fused == (allreduce == "peer")
             if name == "f32":
                 assert maxabs <= f32_tol and ferr <= f32_tol
             else:
