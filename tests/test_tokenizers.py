@@ -11,7 +11,9 @@ import rustygradients_b200 as rg
 from oracle import tokenizer_oracle as T
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-REF_BPE = "/root/reference/bpe_tokenizer_1024.json"  # only where the reference tree is mounted
+# the vocabulary file the reference ships, where its tree sits next to this repository (or RG_REFERENCE_DIR points at it)
+REF_BPE = os.path.join(os.environ.get("RG_REFERENCE_DIR", os.path.join(os.path.dirname(GOLDEN), "..", "..", "reference")),
+                       "bpe_tokenizer_1024.json")
 
 
 def test_reference_kats_char():
