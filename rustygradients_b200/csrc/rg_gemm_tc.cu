@@ -5,8 +5,9 @@
 //
 // This is Linear::forward (src/nn/linear.rs:50-56) on all rows of a prompt at once,
 // the one place on the path that is a dense contraction.  5th-generation tensor cores:
-//  * operands are staged by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a 4-stage
-//    shared-memory ring, 128x64 bf16 tiles of A and of Wt per stage;
+//  * operands are staged by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a 3-stage
+//    shared-memory ring, 128x64 bf16 tiles of A and of Wt per stage (97 KB per CTA, so two
+//    CTAs share an SM and one's epilogue overlaps the other's MMAs);
 //  * one elected thread issues tcgen05.mma (M=128, N=128, K=16, kind::f16, fp32
 //    accumulate) with shared-memory matrix descriptors; the accumulator lives in TMEM
 //    (128 lanes x 128 columns);
@@ -24,7 +25,7 @@
 #define TC_BM 128
 #define TC_BN 128
 #define TC_BK 64
-#define TC_STAGES 4
+#define TC_STAGES 3
 #define TC_THREADS 192
 #define TC_SPIN_LIMIT (1u << 22)
 #define TC_STAGE_BYTES ((TC_BM + TC_BN) * TC_BK * 2)
@@ -72,7 +73,7 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
     return d;
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, 2)
 rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const tc_epi e) {
     extern __shared__ unsigned char tc_smem_raw[];
     // 1024-byte aligned tiles (the swizzle pattern is a function of the address)
@@ -184,15 +185,44 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 float* Cz = e.C + (size_t)blockIdx.z * e.M * e.ldc;
                 if (m < e.M) {
+                    const int nc = n0 + c * 32;
+                    float* crow = Cz + (long long)m * e.ldc + nc;
+                    const float* rrow = e.res ? e.res + (long long)m * e.ldres + nc : nullptr;
+                    // a thread holds 32 consecutive columns of its row: 128 contiguous bytes, moved as 8 x 16 bytes when
+                    // the row segment, the bias and the residual are 16-byte aligned and entirely inside the matrix
+                    const bool vec = nc + 32 <= e.N && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0) &&
+                                     (!e.bias || (reinterpret_cast<uintptr_t>(e.bias + nc) & 15) == 0) &&
+                                     (!rrow || (reinterpret_cast<uintptr_t>(rrow) & 15) == 0);
+                    if (vec) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int n = n0 + c * 32 + j;
-                        if (n < e.N) {
-                            float v = __uint_as_float(r[j]);
-                            if (e.bias) v += e.bias[n];
-                            if (e.act >= 0) v = rg_apply_act(v, e.act);
-                            if (e.res) v += e.res[(long long)m * e.ldres + n];
-                            Cz[(long long)m * e.ldc + n] = v;
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                                   __uint_as_float(r[j + 3]));
+                            if (e.bias) {
+                                const float4 b = __ldg(reinterpret_cast<const float4*>(e.bias + nc + j));
+                                v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
+                            }
+                            if (e.act >= 0) {
+                                v.x = rg_apply_act(v.x, e.act), v.y = rg_apply_act(v.y, e.act);
+                                v.z = rg_apply_act(v.z, e.act), v.w = rg_apply_act(v.w, e.act);
+                            }
+                            if (rrow) {
+                                const float4 q4 = *reinterpret_cast<const float4*>(rrow + j);
+                                v.x += q4.x, v.y += q4.y, v.z += q4.z, v.w += q4.w;
+                            }
+                            *reinterpret_cast<float4*>(crow + j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const int n = nc + j;
+                            if (n < e.N) {
+                                float v = __uint_as_float(r[j]);
+                                if (e.bias) v += e.bias[n];
+                                if (e.act >= 0) v = rg_apply_act(v, e.act);
+                                if (rrow) v += rrow[j];
+                                crow[j] = v;
+                            }
                         }
                     }
                 }
