@@ -276,3 +276,35 @@ def test_persistent_kernel_equals_graph_step(backend, monkeypatch):
         assert backend.launch_count - l0 <= 3                    # one launch for 30 token steps
         tr_rows = a.read_trace()
         assert tr_rows.shape[1] == 12
+
+
+# ---- the whole context window: every position up to block_size, both token-step implementations
+@pytest.mark.parametrize("dtype,B", [("f32", 1), ("bf16", 4)])
+def test_full_context_window(backend, monkeypatch, dtype, B):
+    """GPT-2-small shape (the benchmark workload) driven to the last position of its 1024-token window: the
+    persistent kernel (attention slices grow from one ring chunk to several) against the CUDA-graph step,
+    teacher-forced on the persistent kernel's own ids; then the window is full."""
+    cfg = O.CONFIGS[1]["cfg"]
+    params = O.make_params(cfg, O.config_seed(1), bf16=(dtype == "bf16"))
+    P = 24
+    prompt = O.make_prompt(cfg, O.config_seed(1), B, P)
+    monkeypatch.delenv("RG_B200_DECODE", raising=False)
+    a = model_for(backend, cfg, params, dtype=dtype, max_batch=B)
+    G = cfg.block_size - P + 1                                  # the last id is picked at position block_size - 1
+    out = a.generate(prompt, G)
+    assert out.shape == (B, G) and np.array_equal(out, a.generate(prompt, G))
+    with pytest.raises(rg.ContextFull):
+        a.generate(prompt, G + 1)
+    monkeypatch.setenv("RG_B200_DECODE", "graph")
+    b = model_for(backend, cfg, params, dtype=dtype, max_batch=B)
+    monkeypatch.delenv("RG_B200_DECODE", raising=False)
+    ids = np.concatenate([prompt, out], 1)[:, :cfg.block_size]
+    lb, pb = teacher_forced(b, ids, P)                          # logits that predict ids[:, P:], graph step
+    tol = 1e-4 if dtype == "f32" else 2e-3
+    sure = confident_rows(lb, 10 * tol)
+    assert np.array_equal(pb[sure], ids[:, P:][sure])           # same picks wherever the top-2 gap is clear
+    assert sure.mean() > 0.5
+    la, pa = teacher_forced(a, ids, P)                          # the same steps, one launch of the persistent kernel each
+    assert np.abs(la - lb).max() <= tol
+    assert np.array_equal(pa, la.argmax(-1))
+    assert np.array_equal(pa, out[:, :G - 1])                   # stepwise picks == the ids of the single long run
