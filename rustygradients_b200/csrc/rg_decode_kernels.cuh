@@ -414,11 +414,14 @@ static __global__ void __launch_bounds__(1024) rg_pick_kernel(rg_pick_args p) {
 
 // Merge of the split-context attention partials into finished head outputs:
 // out[b][h*hd + d] = sum_s w_s o_s[d] / sum_s w_s l_s with w_s = exp(m_s - max m).
-static __global__ void rg_attn_merge_kernel(const float* __restrict__ ap, float* __restrict__ out, int B, int H, int hd, int NS) {
+static __global__ void rg_attn_merge_kernel(const float* __restrict__ ap, float* __restrict__ out, int B, int H, int hd, int NS,
+                                            __nv_bfloat16* __restrict__ out16 = nullptr) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= B * H * hd) return;
     rg_vec_in in;
     in.kind = RG_IN_ATTN, in.ap = ap, in.H = H, in.hd = hd, in.NS = NS;
     const int b = i / (H * hd), k = i - b * (H * hd);
-    out[i] = rg_vec_in_value(in, B, H * hd, b, k);
+    const float v = rg_vec_in_value(in, B, H * hd, b, k);
+    if (out) out[i] = v;
+    if (out16) out16[i] = __float2bfloat16_rn(v);  // the input rows of a tensor-core projection
 }

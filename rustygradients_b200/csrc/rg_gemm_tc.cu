@@ -277,8 +277,9 @@ static size_t g_ws_bytes[64];
 // many SMs at once; the partial tiles are summed, in a fixed order, by a second kernel that also applies
 // the epilogue.  The split-k workspace is allocated on first use per device (not inside a stream capture:
 // the prompt pass, which always runs first, goes through here too).
-rg_status rg_gemm_bf16_tc(rg_ctx* ctx, const void* A16, int M, int K, const void* Wt16, int N, float* C, long long ldc,
-                          const float* bias, const float* res, long long ldres, int act) {
+static rg_status tc_gemm(rg_ctx* ctx, const void* A16, int M, int K, const void* Wt16, int N, float* C, long long ldc,
+                         const float* bias, const float* res, long long ldres, int act, const float** raw_parts, int* raw_nparts) {
+    const bool raw = raw_parts != nullptr;
     if (K % TC_BK != 0 || K < TC_BK || M <= 0 || N <= 0) return RG_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(A16) & 15) || (reinterpret_cast<uintptr_t>(Wt16) & 15)) return RG_ERR_UNSUPPORTED;
     if (!g_encode) {
@@ -331,18 +332,35 @@ rg_status rg_gemm_bf16_tc(rg_ctx* ctx, const void* A16, int M, int K, const void
             }
         }
     }
-    if (splits > 1) {
+    if (raw) {
+        // the caller sums the partial tiles itself (fused with what follows the projection)
+        if (g_ws_bytes[ctx->device & 63] < (size_t)splits * M * N * 4) return RG_ERR_UNSUPPORTED;
+        e.C = g_ws[ctx->device & 63], e.ldc = N, e.bias = nullptr, e.res = nullptr, e.act = -1;
+        *raw_parts = e.C, *raw_nparts = splits;
+    } else if (splits > 1) {
         e.C = g_ws[ctx->device & 63], e.ldc = N, e.bias = nullptr, e.res = nullptr, e.act = -1;
     }
     dim3 grid(rg_cdiv(N, TC_BN), rg_cdiv(M, TC_BM), splits);
     rg_gemm_tc_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(tmA, tmB, e);
     RG_CUDA(cudaGetLastError());
     RG_LAUNCHED(ctx);
-    if (splits > 1) {
+    if (splits > 1 && !raw) {
         tc_splitk_reduce_kernel<<<rg_cdiv((long long)M * N, 256), 256, 0, ctx->stream>>>(g_ws[ctx->device & 63], splits, M, N, C, ldc,
                                                                                          bias, res, ldres, act);
         RG_CUDA(cudaGetLastError());
         RG_LAUNCHED(ctx);
     }
     return RG_OK;
+}
+
+rg_status rg_gemm_bf16_tc(rg_ctx* ctx, const void* A16, int M, int K, const void* Wt16, int N, float* C, long long ldc,
+                          const float* bias, const float* res, long long ldres, int act) {
+    return tc_gemm(ctx, A16, M, K, Wt16, N, C, ldc, bias, res, ldres, act, nullptr, nullptr);
+}
+
+// Raw form for few rows: the accumulators of every k-split go to the per-device workspace as [nparts][M][N] (no bias,
+// no activation); the caller's next kernel adds them up in order.  The workspace is reused by the next call.
+rg_status rg_gemm_bf16_tc_parts(rg_ctx* ctx, const void* A16, int M, int K, const void* Wt16, int N, const float** parts,
+                                int* nparts) {
+    return tc_gemm(ctx, A16, M, K, Wt16, N, nullptr, N, nullptr, nullptr, 0, -1, parts, nparts);
 }

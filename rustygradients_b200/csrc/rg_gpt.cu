@@ -6,6 +6,7 @@
 #include "rg_gemm.cuh"
 #include "rg_decode_kernels.cuh"
 #include "rg_prefill_kernels.cuh"
+#include "rg_rows_kernels.cuh"
 #include "rg_sample.cuh"
 
 #include <math.h>
@@ -963,6 +964,70 @@ static rg_status step_ready(rg_gpt* m, size_t steps) {
     return RG_OK;
 }
 
+// The same step with every small kernel between two projections folded into one: the tensor-core GEMM leaves raw
+// k-split partial tiles, the attention kernel sums the q/k/v partials itself, and one kernel per projection does
+// "sum partials + bias (+ residual + next LayerNorm | + activation) -> bf16 rows".  9 launches per block instead of 16.
+static bool rows_tc_usable(const rg_gpt* m) {
+    if (!(m->bf16 && m->use_tc && m->tp_size == 1 && m->pa16) || m->D > RG_ROWS_MAX_D || m->D % 64 || m->F % 64) return false;
+    for (const rg_layer& y : m->layers)
+        if (!y.qkv.Wt || !y.o.Wt || !y.fc1.Wt || !y.fc2.Wt) return false;
+    return m->head.Wt != nullptr;
+}
+static int enqueue_step_rows_tc(rg_gpt* m, int B) {
+    cudaStream_t s = m->ctx->stream;
+    const uint64_t l0 = m->ctx->launches;
+    const int D = m->D, F = m->F, act = m->cfg.activation;
+    __nv_bfloat16* a16 = (__nv_bfloat16*)m->pa16;
+    rg_embed_step_kernel<__nv_bfloat16><<<B, 128, 0, s>>>(m->tokens, m->C, (const __nv_bfloat16*)m->wte, (const __nv_bfloat16*)m->wpe,
+                                                          D, m->ldt, m->px, m->d_pos_next, m->d_pos);
+    rg_rows_res_ln_bf16_kernel<<<B, 256, 0, s>>>(nullptr, 0, 0, nullptr, m->px, 0, m->layers[0].ln1g, m->layers[0].ln1b, a16, D);
+    m->ctx->launches += 2;
+    // context slices per (sequence, head): enough CTAs to fill the GPU a few times over, no more
+    const int NS = std::max(1, std::min(m->NS, rg_cdiv(4 * m->ctx->sm_count, B * m->Hl)));
+    const float* parts = nullptr;
+    int np = 0;
+    for (int l = 0; l < m->L; l++) {
+        rg_layer& y = m->layers[l];
+        if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, D, y.qkv.Wt, 3 * D, &parts, &np) != RG_OK) return -1;
+        {
+            rg_attn_step_args a;
+            a.qkv_parts = parts, a.nparts = np, a.qkv_bias = y.qkv.b;
+            a.kcache = m->kc + (size_t)l * m->kv_layer_bytes, a.vcache = m->vc + (size_t)l * m->kv_layer_bytes;
+            a.ap = m->ap, a.pos = m->d_pos;
+            a.B = B, a.H = m->Hl, a.C = m->C, a.D = m->Dl, a.NS = NS;
+            a.scale = 1.f / sqrtf((float)m->hd);
+            dim3 grid(NS, m->Hl, B);
+            if (m->hd == 32) rg_attn_step_kernel<__nv_bfloat16, 32><<<grid, 128, 0, s>>>(a);
+            else if (m->hd == 64) rg_attn_step_kernel<__nv_bfloat16, 64><<<grid, 128, 0, s>>>(a);
+            else rg_attn_step_kernel<__nv_bfloat16, 128><<<grid, 128, 0, s>>>(a);
+            rg_attn_merge_kernel<<<rg_cdiv(B * D, 256), 256, 0, s>>>(m->ap, nullptr, B, m->Hl, m->hd, NS, a16);
+            m->ctx->launches += 2;
+        }
+        if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, D, y.o.Wt, D, &parts, &np) != RG_OK) return -1;
+        rg_rows_res_ln_bf16_kernel<<<B, 256, 0, s>>>(parts, np, (size_t)B * D, y.o.b, m->px, 1, y.ln2g, y.ln2b, a16, D);
+        RG_LAUNCHED(m->ctx);
+        if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, D, y.fc1.Wt, F, &parts, &np) != RG_OK) return -1;
+        rg_rows_act_bf16_kernel<<<rg_cdiv((long long)B * F, 256), 256, 0, s>>>(parts, np, (size_t)B * F, y.fc1.b, F, (size_t)B * F, act,
+                                                                           a16);
+        RG_LAUNCHED(m->ctx);
+        if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, F, y.fc2.Wt, D, &parts, &np) != RG_OK) return -1;
+        const bool last = l + 1 == m->L;
+        rg_rows_res_ln_bf16_kernel<<<B, 256, 0, s>>>(parts, np, (size_t)B * D, y.fc2.b, m->px, 1, last ? m->lnfg : m->layers[l + 1].ln1g,
+                                                      last ? m->lnfb : m->layers[l + 1].ln1b, a16, D);
+        RG_LAUNCHED(m->ctx);
+    }
+    if (rg_gemm_bf16_tc(m->ctx, a16, B, D, m->head.Wt, m->V, m->logits, m->V, m->head.b, nullptr, 0, -1) != RG_OK) return -1;
+    rg_pick_args pa;
+    pa.parts = m->logits, pa.nparts = 1, pa.bias = nullptr, pa.logits = m->logits;
+    pa.tokens = m->tokens, pa.picks = m->picks, pa.pos = m->d_pos, pa.pos_next = m->d_pos_next;
+    pa.B = B, pa.V = m->V, pa.C = m->C;
+    rg_pick_kernel<<<B, 1024, 0, s>>>(pa);
+    RG_LAUNCHED(m->ctx);
+    const int n = (int)(m->ctx->launches - l0);
+    m->ctx->launches = l0;
+    return n;
+}
+
 static rg_status run_steps(rg_gpt* m, size_t steps) {
     const int B = (int)m->curB;
     cudaStream_t s = m->ctx->stream;
@@ -982,9 +1047,12 @@ static rg_status run_steps(rg_gpt* m, size_t steps) {
         RG_TRY(ensure_rows(m, (size_t)std::max(B, 128)));
         RG_TRY(ensure_gather(m, B));
     }
+    const char* rows_env = getenv("RG_B200_ROWS_STEP");  // "plain": one kernel per operation (for comparisons)
+    const bool fuse_env = !(rows_env && strcmp(rows_env, "plain") == 0);
+    const bool rows_fused = rows_path && fuse_env && rows_tc_usable(m);
     if (!m->use_graph) {
         for (size_t i = 0; i < steps; i++) {
-            const int n = rows_path ? enqueue_step_rows(m, B) : enqueue_step(m, B);
+            const int n = rows_path ? (rows_fused ? enqueue_step_rows_tc(m, B) : enqueue_step_rows(m, B)) : enqueue_step(m, B);
             if (n < 0) return RG_ERR_BACKEND;
             m->ctx->launches += n;
             RG_CUDA(cudaGetLastError());
@@ -994,7 +1062,8 @@ static rg_status run_steps(rg_gpt* m, size_t steps) {
             if (m->graph) cudaGraphExecDestroy(m->graph), m->graph = nullptr;
             cudaGraph_t gr = nullptr;
             RG_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-            m->kernels_per_step = rows_path ? enqueue_step_rows(m, B) : enqueue_step(m, B);
+            m->kernels_per_step =
+                rows_path ? (rows_fused ? enqueue_step_rows_tc(m, B) : enqueue_step_rows(m, B)) : enqueue_step(m, B);
             cudaError_t e = cudaStreamEndCapture(s, &gr);
             if (m->kernels_per_step < 0) {
                 if (gr) cudaGraphDestroy(gr);

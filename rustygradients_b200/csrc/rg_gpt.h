@@ -83,6 +83,9 @@ struct rg_gpt {
 rg_status rg_gemm_bf16_tc(rg_ctx* ctx, const void* A16, int M, int K, const void* Wt16, int N, float* C, long long ldc,
                           const float* bias, const float* res, long long ldres, int act);
 
+rg_status rg_gemm_bf16_tc_parts(rg_ctx* ctx, const void* A16, int M, int K, const void* Wt16, int N, const float** parts,
+                                int* nparts);
+
 // rg_mega.cu
 rg_status rg_mega_create(rg_gpt* m);            // after the weights are on the device
 void rg_mega_destroy(rg_gpt* m);

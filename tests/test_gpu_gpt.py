@@ -308,3 +308,25 @@ def test_full_context_window(backend, monkeypatch, dtype, B):
     assert np.abs(la - lb).max() <= tol
     assert np.array_equal(pa, la.argmax(-1))
     assert np.array_equal(pa, out[:, :G - 1])                   # stepwise picks == the ids of the single long run
+
+
+# ---- the GEMM-form token step (batch >= 8, bf16): fused kernels between the projections == one kernel per operation
+def test_fused_rows_step_equals_plain_rows_step(backend, monkeypatch):
+    cfg = O.GptConfig(64, 1000, 2, 4, 256)
+    params = O.make_params(cfg, 23, stress=True, bf16=True)
+    for B in (8, 19):
+        prompt = O.make_prompt(cfg, 23 + B, B, 9)
+        monkeypatch.delenv("RG_B200_ROWS_STEP", raising=False)
+        a = model_for(backend, cfg, params, dtype="bf16", max_batch=B)
+        ids = np.concatenate([prompt, a.generate(prompt, 20)], 1)
+        la, pa = teacher_forced(a, ids, 9)
+        monkeypatch.setenv("RG_B200_ROWS_STEP", "plain")
+        b = model_for(backend, cfg, params, dtype="bf16", max_batch=B)
+        lb, pb = teacher_forced(b, ids, 9)
+        monkeypatch.delenv("RG_B200_ROWS_STEP", raising=False)
+        scale = np.abs(lb).max(-1, keepdims=True)
+        # same arithmetic up to the order of the f32 sums, which moves some activations by one bf16 step (2^-8 relative)
+        assert (np.abs(la - lb) / scale).max() <= 8e-3
+        assert np.array_equal(pa, la.argmax(-1)) and np.array_equal(pb, lb.argmax(-1))
+        want = O.teacher_forced_logits(params, cfg, ids, True, "gelu_tanh", 9)
+        assert (np.abs(la - want) / np.abs(want).max(-1, keepdims=True)).max() <= BF16_REL_TOL
