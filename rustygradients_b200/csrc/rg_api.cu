@@ -80,6 +80,7 @@ extern "C" rg_status rg_ctx_destroy(rg_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     cudaStreamDestroy(ctx->stream);
     cudaFree(ctx->d_flag);
+    cudaFree(ctx->tc_ws);
     cudaFreeHost(ctx->h_flag);
     delete ctx;
     return RG_OK;

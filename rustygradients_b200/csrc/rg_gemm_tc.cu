@@ -269,13 +269,11 @@ static __global__ void tc_splitk_reduce_kernel(const float* __restrict__ ws, int
     C[(long long)m * ldc + n] = v;
 }
 
-static float* g_ws[64];
-static size_t g_ws_bytes[64];
 
 // Returns RG_ERR_UNSUPPORTED (without touching C) when the shape is outside the kernel's limits.
 // With few rows (one M tile) the k range is split over several CTAs so that the weights stream through
 // many SMs at once; the partial tiles are summed, in a fixed order, by a second kernel that also applies
-// the epilogue.  The split-k workspace is allocated on first use per device (not inside a stream capture:
+// the epilogue.  The split-k workspace is allocated on first use per context (not inside a stream capture:
 // the prompt pass, which always runs first, goes through here too).
 static rg_status tc_gemm(rg_ctx* ctx, const void* A16, int M, int K, const void* Wt16, int N, float* C, long long ldc,
                          const float* bias, const float* res, long long ldres, int act, const float** raw_parts, int* raw_nparts) {
@@ -294,12 +292,11 @@ static rg_status tc_gemm(rg_ctx* ctx, const void* A16, int M, int K, const void*
         cudaError_t ea = cudaFuncSetAttribute(rg_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
         if (ea != cudaSuccess) return rg_fail(RG_ERR_BACKEND, "rg_gemm_tc_kernel: %s", cudaGetErrorString(ea));
     }
-    {   // split-k workspace of this device: 64 MiB on the first call (the prompt pass, never inside a capture)
-        const int dev = ctx->device & 63;
+    {   // split-k workspace of this context: 64 MiB on the first call (the prompt pass, never inside a capture)
         cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
         cudaStreamIsCapturing(ctx->stream, &cs);
-        if (!g_ws[dev] && cs == cudaStreamCaptureStatusNone) {
-            if (cudaMalloc(&g_ws[dev], (size_t)64 << 20) == cudaSuccess) g_ws_bytes[dev] = (size_t)64 << 20;
+        if (!ctx->tc_ws && cs == cudaStreamCaptureStatusNone) {
+            if (cudaMalloc(&ctx->tc_ws, (size_t)64 << 20) == cudaSuccess) ctx->tc_ws_bytes = (size_t)64 << 20;
             else cudaGetLastError();
         }
     }
@@ -317,35 +314,34 @@ static rg_status tc_gemm(rg_ctx* ctx, const void* A16, int M, int K, const void*
     e.err = ctx->d_flag + 1;
     if (splits > 1) {
         const size_t need = (size_t)splits * M * N * 4;
-        const int dev = ctx->device & 63;
-        if (g_ws_bytes[dev] < need) {
+        if (ctx->tc_ws_bytes < need) {
             cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
             cudaStreamIsCapturing(ctx->stream, &cs);
             if (cs != cudaStreamCaptureStatusNone) {
                 splits = 1, e.kb_per_split = nkb;  // cannot allocate now: run unsplit
             } else {
                 const size_t want = std::max(need, (size_t)64 << 20);
-                if (g_ws[dev]) cudaFree(g_ws[dev]);
-                g_ws[dev] = nullptr, g_ws_bytes[dev] = 0;
-                if (cudaMalloc(&g_ws[dev], want) == cudaSuccess) g_ws_bytes[dev] = want;
+                if (ctx->tc_ws) cudaFree(ctx->tc_ws);
+                ctx->tc_ws = nullptr, ctx->tc_ws_bytes = 0;
+                if (cudaMalloc(&ctx->tc_ws, want) == cudaSuccess) ctx->tc_ws_bytes = want;
                 else cudaGetLastError(), splits = 1, e.kb_per_split = nkb;
             }
         }
     }
     if (raw) {
         // the caller sums the partial tiles itself (fused with what follows the projection)
-        if (g_ws_bytes[ctx->device & 63] < (size_t)splits * M * N * 4) return RG_ERR_UNSUPPORTED;
-        e.C = g_ws[ctx->device & 63], e.ldc = N, e.bias = nullptr, e.res = nullptr, e.act = -1;
+        if (ctx->tc_ws_bytes < (size_t)splits * M * N * 4) return RG_ERR_UNSUPPORTED;
+        e.C = ctx->tc_ws, e.ldc = N, e.bias = nullptr, e.res = nullptr, e.act = -1;
         *raw_parts = e.C, *raw_nparts = splits;
     } else if (splits > 1) {
-        e.C = g_ws[ctx->device & 63], e.ldc = N, e.bias = nullptr, e.res = nullptr, e.act = -1;
+        e.C = ctx->tc_ws, e.ldc = N, e.bias = nullptr, e.res = nullptr, e.act = -1;
     }
     dim3 grid(rg_cdiv(N, TC_BN), rg_cdiv(M, TC_BM), splits);
     rg_gemm_tc_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(tmA, tmB, e);
     RG_CUDA(cudaGetLastError());
     RG_LAUNCHED(ctx);
     if (splits > 1 && !raw) {
-        tc_splitk_reduce_kernel<<<rg_cdiv((long long)M * N, 256), 256, 0, ctx->stream>>>(g_ws[ctx->device & 63], splits, M, N, C, ldc,
+        tc_splitk_reduce_kernel<<<rg_cdiv((long long)M * N, 256), 256, 0, ctx->stream>>>(ctx->tc_ws, splits, M, N, C, ldc,
                                                                                          bias, res, ldres, act);
         RG_CUDA(cudaGetLastError());
         RG_LAUNCHED(ctx);

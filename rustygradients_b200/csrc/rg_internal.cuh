@@ -46,6 +46,8 @@ struct rg_ctx {
     uint64_t launches = 0;
     int* d_flag = nullptr;  // device word kernels raise on invalid input
     int* h_flag = nullptr;  // pinned mirror
+    float* tc_ws = nullptr;  // split-k workspace of the tensor-core GEMM (this context's stream only)
+    size_t tc_ws_bytes = 0;
 };
 
 struct rg_devbuf {
