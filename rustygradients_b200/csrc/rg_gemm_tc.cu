@@ -5,12 +5,12 @@
 //
 // This is Linear::forward (src/nn/linear.rs:50-56) on all rows of a prompt at once,
 // the one place on the path that is a dense contraction.  5th-generation tensor cores:
-//  * operands are staged by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a 3-stage
-//    shared-memory ring, 128x64 bf16 tiles of A and of Wt per stage (97 KB per CTA, so two
-//    CTAs share an SM and one's epilogue overlaps the other's MMAs);
+//  * one CTA per SM walks the output tiles (persistent); operands are staged by TMA
+//    (cp.async.bulk.tensor, 128-byte swizzle) into a 6-stage shared-memory ring, 128x64 bf16
+//    tiles of A and of Wt per stage, and the producer runs ahead across tile boundaries;
 //  * one elected thread issues tcgen05.mma (M=128, N=128, K=16, kind::f16, fp32
-//    accumulate) with shared-memory matrix descriptors; the accumulator lives in TMEM
-//    (128 lanes x 128 columns);
+//    accumulate) with shared-memory matrix descriptors; two accumulators live in TMEM
+//    (128 lanes x 128 columns each), so the epilogue of a tile overlaps the MMAs of the next;
 //  * tcgen05.commit signals "stage consumed" and "accumulator complete" on mbarriers;
 //  * four epilogue warps read the accumulator back with tcgen05.ld (32 lanes x 32
 //    columns at a time) and apply bias / activation / residual on the way to HBM.
@@ -25,7 +25,7 @@
 #define TC_BM 128
 #define TC_BN 128
 #define TC_BK 64
-#define TC_STAGES 3
+#define TC_STAGES 6
 #define TC_THREADS 192
 #define TC_SPIN_LIMIT (1u << 22)
 #define TC_STAGE_BYTES ((TC_BM + TC_BN) * TC_BK * 2)
@@ -73,18 +73,20 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
     return d;
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 2)
+__global__ void __launch_bounds__(TC_THREADS, 1)
 rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const tc_epi e) {
     extern __shared__ unsigned char tc_smem_raw[];
     // 1024-byte aligned tiles (the swizzle pattern is a function of the address)
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + TC_STAGES * TC_STAGE_BYTES);
     uint64_t* empty = full + TC_STAGES;
-    uint64_t* acc_full = empty + TC_STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    uint64_t* acc_full = empty + TC_STAGES;  // [2]: accumulator b holds a finished tile
+    uint64_t* acc_empty = acc_full + 2;      // [2]: the epilogue warps have read accumulator b
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
+    const int tiles_n = (e.N + TC_BN - 1) / TC_BN, tiles_m = (e.M + TC_BM - 1) / TC_BM;
+    const int ntiles = tiles_n * tiles_m;
     const int kb_begin = blockIdx.z * e.kb_per_split;
     const int nkb = min(e.kb_per_split, e.K / TC_BK - kb_begin);
 
@@ -93,11 +95,14 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&full[s])) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&empty[s])) : "memory");
         }
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(acc_full)) : "memory");
+        for (int b = 0; b < 2; b++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&acc_full[b])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(tc_smem(&acc_empty[b])) : "memory");
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // the MMA warp owns the tensor memory: 128 columns of fp32 accumulators
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;" ::"r"(tc_smem(tmem_slot)) : "memory");
+    if (warp == 1) {  // the MMA warp owns the tensor memory: two accumulators of 128 fp32 columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(tc_smem(tmem_slot)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -105,73 +110,96 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
+    // Persistent tile loop: CTA x takes tiles x, x + gridDim.x, ...; n varies fastest, so the CTAs running at the same
+    // time share rows of A in L2.  The three roles walk the same sequence, each with its own counters.
     if (warp == 0) {
-        // ===== TMA producer =====
+        // ===== TMA producer: runs ahead across tile boundaries, up to TC_STAGES k-blocks =====
         if (lane == 0) {
-            for (int kb = 0; kb < nkb; kb++) {
-                const int s = kb % TC_STAGES;
-                const uint32_t par = (kb / TC_STAGES) & 1;
-                if (!tc_wait(&empty[s], par ^ 1u, e.err)) break;
-                unsigned char* a_dst = tiles + s * TC_STAGE_BYTES;
-                unsigned char* b_dst = a_dst + TC_BM * TC_BK * 2;
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full[s])),
-                             "r"((uint32_t)TC_STAGE_BYTES)
-                             : "memory");
-                asm volatile(
-                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                        tc_smem(a_dst)),
-                    "l"(&tmA), "r"((kb_begin + kb) * TC_BK), "r"(m0), "r"(tc_smem(&full[s]))
-                    : "memory");
-                asm volatile(
-                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                        tc_smem(b_dst)),
-                    "l"(&tmB), "r"((kb_begin + kb) * TC_BK), "r"(n0), "r"(tc_smem(&full[s]))
-                    : "memory");
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / tiles_n) * TC_BM, n0 = (tile % tiles_n) * TC_BN;
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = it % TC_STAGES;
+                    const uint32_t par = (it / TC_STAGES) & 1;
+                    ok = tc_wait(&empty[s], par ^ 1u, e.err);
+                    if (!ok) break;
+                    unsigned char* a_dst = tiles + s * TC_STAGE_BYTES;
+                    unsigned char* b_dst = a_dst + TC_BM * TC_BK * 2;
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full[s])),
+                                 "r"((uint32_t)TC_STAGE_BYTES)
+                                 : "memory");
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                            tc_smem(a_dst)),
+                        "l"(&tmA), "r"((kb_begin + kb) * TC_BK), "r"(m0), "r"(tc_smem(&full[s]))
+                        : "memory");
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                            tc_smem(b_dst)),
+                        "l"(&tmB), "r"((kb_begin + kb) * TC_BK), "r"(n0), "r"(tc_smem(&full[s]))
+                        : "memory");
+                }
             }
         }
     } else if (warp == 1) {
-        // ===== MMA issuer =====
+        // ===== MMA issuer: accumulator (tile count & 1), so the epilogue of one tile overlaps the MMAs of the next =====
         if (lane == 0) {
             // instruction descriptor: D = f32, A = B = bf16, both K-major, N = 128, M = 128
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            uint32_t it = 0, tl = 0;
             bool ok = true;
-            for (int kb = 0; kb < nkb && ok; kb++) {
-                const int s = kb % TC_STAGES;
-                const uint32_t par = (kb / TC_STAGES) & 1;
-                ok = tc_wait(&full[s], par, e.err);
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, tl++) {
+                const uint32_t buf = tl & 1u, use = tl >> 1;
+                ok = tc_wait(&acc_empty[buf], (use & 1u) ^ 1u, e.err);  // passes at once for the first use of a buffer
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = tc_smem(tiles + s * TC_STAGE_BYTES);
-                const uint32_t b_addr = a_addr + TC_BM * TC_BK * 2;
+                const uint32_t d_tmem = tmem_base + buf * TC_BN;
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int s = it % TC_STAGES;
+                    const uint32_t par = (it / TC_STAGES) & 1;
+                    ok = tc_wait(&full[s], par, e.err);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = tc_smem(tiles + s * TC_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + TC_BM * TC_BK * 2;
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; k++) {
-                    const uint64_t da = tc_desc(a_addr + k * 32);  // 16 bf16 = 32 bytes further along K inside the swizzle span
-                    const uint64_t db = tc_desc(b_addr + k * 32);
-                    const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-                    asm volatile(
-                        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_base),
-                        "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-                        : "memory");
+                    for (int k = 0; k < TC_BK / 16; k++) {
+                        const uint64_t da = tc_desc(a_addr + k * 32);  // 16 bf16 = 32 bytes further along K inside the swizzle span
+                        const uint64_t db = tc_desc(b_addr + k * 32);
+                        const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                            "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+                            : "memory");
+                    }
+                    // the stage is free again once these MMAs have read it
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&empty[s]))
+                                 : "memory");
                 }
-                // the stage is free again once these MMAs have read it
-                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&empty[s]))
-                             : "memory");
+                if (ok)
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                     tc_smem(&acc_full[buf]))
+                                 : "memory");
             }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(acc_full))
-                         : "memory");
         }
     } else {
         // ===== epilogue warps 2..5: TMEM lane quarter = warp % 4 =====
         const int q = warp & 3;
-        const bool ok = tc_wait(acc_full, 0, e.err);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int m = m0 + q * 32 + lane;
-        if (ok) {
+        uint32_t tl = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, tl++) {
+            const int m0 = (tile / tiles_n) * TC_BM, n0 = (tile % tiles_n) * TC_BN;
+            const uint32_t buf = tl & 1u, use = tl >> 1;
+            ok = tc_wait(&acc_full[buf], use & 1u, e.err);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int m = m0 + q * 32 + lane;
 #pragma unroll 1
             for (int c = 0; c < TC_BN / 32; c++) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32);
+                const uint32_t taddr = tmem_base + buf * TC_BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -183,6 +211,12 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (c == TC_BN / 32 - 1) {
+                    // every column of this accumulator has been read: hand it back before the last stores
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&acc_empty[buf])) : "memory");
+                }
                 float* Cz = e.C + (size_t)blockIdx.z * e.M * e.ldc;
                 if (m < e.M) {
                     const int nc = n0 + c * 32;
@@ -231,7 +265,7 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" ::"r"(tmem_base) : "memory");
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
 }
 
 // ---------------------------------------------------------------------------
@@ -336,7 +370,7 @@ static rg_status tc_gemm(rg_ctx* ctx, const void* A16, int M, int K, const void*
     } else if (splits > 1) {
         e.C = ctx->tc_ws, e.ldc = N, e.bias = nullptr, e.res = nullptr, e.act = -1;
     }
-    dim3 grid(rg_cdiv(N, TC_BN), rg_cdiv(M, TC_BM), splits);
+    dim3 grid(std::min(ntiles, ctx->sm_count), 1, splits);  // persistent: one CTA per SM walks the tiles
     rg_gemm_tc_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(tmA, tmB, e);
     RG_CUDA(cudaGetLastError());
     RG_LAUNCHED(ctx);

@@ -163,6 +163,38 @@ static __global__ void rg_transpose_bf16_kernel(const __nv_bfloat16* __restrict_
         if (n < N && k < K) Wt[(size_t)n * K + k] = t[threadIdx.x][i];
     }
 }
+// f32 mode: Wt3[n][0:K] = hi(W[k][n]), [K:2K] = lo, [2K:3K] = hi
+static __global__ void rg_split3_wt_kernel(const float* __restrict__ W, long long ldw, int K, int N, __nv_bfloat16* __restrict__ Wt3) {
+    __shared__ float t[32][33];
+    const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int k = k0 + i, n = n0 + threadIdx.x;
+        t[i][threadIdx.x] = (k < K && n < N) ? W[(size_t)k * ldw + n] : 0.f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int n = n0 + i, k = k0 + threadIdx.x;
+        if (n < N && k < K) {
+            const float w = t[threadIdx.x][i];
+            const __nv_bfloat16 hi = __float2bfloat16_rn(w);
+            const __nv_bfloat16 lo = __float2bfloat16_rn(w - __bfloat162float(hi));
+            __nv_bfloat16* row = Wt3 + (size_t)n * 3 * K;
+            row[k] = hi, row[K + k] = lo, row[2 * K + k] = hi;
+        }
+    }
+}
+// f32 mode: A3[m][0:K] = hi(A[m][k]), [K:2K] = hi, [2K:3K] = lo
+static __global__ void rg_split3_rows_kernel(const float* __restrict__ A, int K, size_t total, __nv_bfloat16* __restrict__ A3) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t mrow = i / K;
+    const int k = (int)(i - mrow * K);
+    const float a = A[i];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(a);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(a - __bfloat162float(hi));
+    __nv_bfloat16* row = A3 + mrow * 3 * K;
+    row[k] = hi, row[K + k] = hi, row[2 * K + k] = lo;
+}
 static __global__ void rg_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, size_t n) {
     size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i + 3 < n) {
@@ -217,7 +249,10 @@ static rg_status alloc_linear(rg_gpt* m, rg_linear& lin, int K, int N) {
     RG_TRY(dalloc(m, &lin.W, (size_t)K * lin.ldw * m->wsize));
     RG_CUDA(cudaMemset(lin.W, 0, (size_t)K * lin.ldw * m->wsize));
     RG_TRY(dalloc(m, (void**)&lin.b, (size_t)N * 4));
-    if (m->bf16 && m->use_tc && K % 64 == 0) RG_TRY(dalloc(m, &lin.Wt, (size_t)N * K * 2));
+    // K-contiguous copy for the tensor-core GEMM.  bf16 mode: Wt[n][k].  f32 mode: Wt[n][3K] = [hi | lo | hi] with
+    // w = hi + lo + O(2^-17 w) in bf16 pieces, multiplied against rows [a_hi | a_hi | a_lo]: three bf16 products
+    // accumulated in fp32 reproduce the f32 product to ~2^-16 relative, well inside the f32-mode tolerance.
+    if (m->use_tc && K % 64 == 0) RG_TRY(dalloc(m, &lin.Wt, (size_t)N * K * (m->bf16 ? 2 : 6)));
     plan_split(m, lin);
     RG_TRY(dalloc(m, (void**)&lin.parts, (size_t)lin.ksplit * m->Bmax * N * 4));
     return RG_OK;
@@ -483,6 +518,18 @@ extern "C" rg_status rg_gpt_load_params(rg_gpt* m, const float* const* data, con
         RG_CUDA(cudaGetLastError());
         RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
     }
+    if (!m->bf16) {  // hi | lo | hi pieces for the f32-accurate tensor-core prompt pass
+        auto sp = [&](rg_linear& lin) {
+            if (!lin.Wt) return;
+            dim3 grid(rg_cdiv(lin.N, 32), rg_cdiv(lin.K, 32)), block(32, 8);
+            rg_split3_wt_kernel<<<grid, block, 0, m->ctx->stream>>>((const float*)lin.W, lin.ldw, lin.K, lin.N, (__nv_bfloat16*)lin.Wt);
+            RG_LAUNCHED(m->ctx);
+        };
+        for (auto& y : m->layers) sp(y.qkv), sp(y.o), sp(y.fc1), sp(y.fc2);
+        sp(m->head);
+        RG_CUDA(cudaGetLastError());
+        RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    }
     m->loaded = true;
     m->pos = 0;
     m->curB = 0;
@@ -511,7 +558,8 @@ static rg_status ensure_rows(rg_gpt* m, size_t rows) {
         m->pwsFloats = (size_t)8 << 20;
         RG_TRY(dalloc(m, (void**)&m->pws, m->pwsFloats * 4));
     }
-    if (m->bf16 && m->use_tc) RG_TRY(dalloc(m, &m->pa16, std::max<size_t>(rows, 128) * (size_t)std::max(m->D, m->Fl) * 2));
+    if (m->use_tc)
+        RG_TRY(dalloc(m, &m->pa16, std::max<size_t>(rows, 128) * (size_t)std::max(m->D, m->Fl) * (m->bf16 ? 2 : 6)));
     RG_TRY(dalloc(m, (void**)&m->plast, (size_t)m->Bmax * m->D * 4));
     m->rowsCap = rows;
     return RG_OK;
@@ -548,6 +596,16 @@ static rg_status gemm(rg_gpt* m, const float* A, int M, const rg_linear& lin, fl
         rg_to_bf16_kernel<<<rg_cdiv((long long)cnt, 1024), 256, 0, m->ctx->stream>>>(A, (__nv_bfloat16*)m->pa16, cnt);
         RG_LAUNCHED(m->ctx);
         rg_status st = rg_gemm_bf16_tc(m->ctx, m->pa16, M, lin.K, lin.Wt, lin.N, Cout, p.ldc, p.bias, res, lin.N, act);
+        if (st == RG_OK) return RG_OK;
+        if (st != RG_ERR_UNSUPPORTED) return st;
+    }
+    if (!m->bf16 && m->use_tc && lin.Wt && m->pa16 && M >= 32) {
+        // f32 mode with enough rows for a tensor tile: split both operands into bf16 pieces (see lin.Wt) and run the
+        // same tcgen05 GEMM over the concatenated K range
+        const size_t cnt = (size_t)M * lin.K;
+        rg_split3_rows_kernel<<<rg_cdiv((long long)cnt, 256), 256, 0, m->ctx->stream>>>(A, lin.K, cnt, (__nv_bfloat16*)m->pa16);
+        RG_LAUNCHED(m->ctx);
+        rg_status st = rg_gemm_bf16_tc(m->ctx, m->pa16, M, 3 * lin.K, lin.Wt, lin.N, Cout, p.ldc, p.bias, res, lin.N, act);
         if (st == RG_OK) return RG_OK;
         if (st != RG_ERR_UNSUPPORTED) return st;
     }
