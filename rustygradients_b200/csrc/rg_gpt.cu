@@ -543,10 +543,10 @@ static rg_status ensure_rows(rg_gpt* m, size_t rows) {
     if (rows <= m->rowsCap) return RG_OK;
     RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
     dfree(m, m->px), dfree(m, m->pln), dfree(m, m->pqkv), dfree(m, m->pattn), dfree(m, m->ph), dfree(m, m->plast);
-    dfree(m, m->ptp), dfree(m, m->pa16);
+    dfree(m, m->ptp), dfree(m, m->pa16), dfree(m, m->pq16), dfree(m, m->pvt16);
     if (m->graph) cudaGraphExecDestroy(m->graph), m->graph = nullptr;  // a captured step may point into the old buffers
     m->px = m->pln = m->pqkv = m->pattn = m->ph = m->plast = m->ptp = nullptr;
-    m->pa16 = nullptr;
+    m->pa16 = m->pq16 = m->pvt16 = nullptr;
     m->rowsCap = 0;
     RG_TRY(dalloc(m, (void**)&m->px, rows * m->D * 4));
     RG_TRY(dalloc(m, (void**)&m->pln, rows * m->D * 4));
@@ -560,6 +560,10 @@ static rg_status ensure_rows(rg_gpt* m, size_t rows) {
     }
     if (m->use_tc)
         RG_TRY(dalloc(m, &m->pa16, std::max<size_t>(rows, 128) * (size_t)std::max(m->D, m->Fl) * (m->bf16 ? 2 : 6)));
+    if (m->bf16 && m->use_tc && m->hd == 64) {
+        RG_TRY(dalloc(m, &m->pq16, rows * m->Dl * 2));
+        RG_TRY(dalloc(m, &m->pvt16, (rows + 64 * (size_t)std::max(m->Bmax, 1)) * m->Dl * 2));
+    }
     RG_TRY(dalloc(m, (void**)&m->plast, (size_t)m->Bmax * m->D * 4));
     m->rowsCap = rows;
     return RG_OK;
@@ -622,9 +626,17 @@ static rg_status attn_rows(rg_gpt* m, int l, int B, int T) {
     const KT* vc = (const KT*)(m->vc + (size_t)l * m->kv_layer_bytes);
     cudaStream_t s = m->ctx->stream;
     rg_kv_scatter_kernel<KT><<<B * T, 256, 0, s>>>(m->pqkv, (KT*)kc, (KT*)vc, T, m->Hl, m->hd, m->C, m->Dl);
+    const int causal = m->cfg.causal ? 1 : 0;
+    if (sizeof(KT) == 2 && m->pq16 && m->pvt16 && B <= std::max(m->Bmax, 1)) {
+        // bf16 mode, head_dim 64: attention of all rows on the tensor cores
+        RG_LAUNCHED(m->ctx);
+        rg_status st = rg_attn_bf16_tc(m->ctx, m->pqkv, kc, B, m->Hl, T, m->C, m->Dl, m->hd, causal, m->pq16, m->pvt16, m->pattn);
+        if (st == RG_OK) return RG_OK;
+        if (st != RG_ERR_UNSUPPORTED) return st;
+        m->ctx->launches -= 1;
+    }
     dim3 grid(rg_cdiv(T, 8), m->Hl, B);
     const float scale = 1.f / sqrtf((float)m->hd);
-    const int causal = m->cfg.causal ? 1 : 0;
     if (m->hd == 32)
         rg_attn_rows_kernel<KT, 32><<<grid, 256, 0, s>>>(m->pqkv, kc, vc, m->pattn, T, m->Hl, m->C, m->Dl, scale, causal);
     else if (m->hd == 64)

@@ -65,6 +65,7 @@ struct rg_gpt {
     // prompt-pass buffers, grown on demand
     size_t rowsCap = 0;
     float *px = nullptr, *pln = nullptr, *pqkv = nullptr, *pattn = nullptr, *ph = nullptr, *plast = nullptr;
+    void *pq16 = nullptr, *pvt16 = nullptr;  // bf16 Q rows and V^T of the tensor-core attention of the prompt pass
     void* pa16 = nullptr;  // bf16 copy of the current GEMM input rows
     float* pws = nullptr;  // split-k workspace of the CUDA-core GEMM
     size_t pwsFloats = 0;
@@ -85,6 +86,10 @@ rg_status rg_gemm_bf16_tc(rg_ctx* ctx, const void* A16, int M, int K, const void
 
 rg_status rg_gemm_bf16_tc_parts(rg_ctx* ctx, const void* A16, int M, int K, const void* Wt16, int N, const float** parts,
                                 int* nparts);
+
+// rg_attn_tc.cu: RG_ERR_UNSUPPORTED when the shape is outside the tensor-core attention kernel's limits
+rg_status rg_attn_bf16_tc(rg_ctx* ctx, const float* qkv, const void* kcache, int B, int H, int T, int C, int D, int hd, int causal,
+                          void* q16, void* vt16, float* out);
 
 // rg_mega.cu
 rg_status rg_mega_create(rg_gpt* m);            // after the weights are on the device

@@ -330,3 +330,34 @@ def test_fused_rows_step_equals_plain_rows_step(backend, monkeypatch):
         assert np.array_equal(pa, la.argmax(-1)) and np.array_equal(pb, lb.argmax(-1))
         want = O.teacher_forced_logits(params, cfg, ids, True, "gelu_tanh", 9)
         assert (np.abs(la - want) / np.abs(want).max(-1, keepdims=True)).max() <= BF16_REL_TOL
+
+
+# ---- prompt pass in bf16 mode: tensor-core projections and attention against the CUDA-core kernels and the oracle
+@pytest.mark.parametrize("causal", [True, False])
+def test_prompt_pass_tensor_core_kernels(backend, monkeypatch, causal):
+    """Ragged sizes on purpose: prompt lengths that are not multiples of the 128-row tiles, a block_size that is not
+    one either (key tiles then run past the end of a head's cache rows), several sequences and heads."""
+    cfg = O.GptConfig(330, 777, 2, 4, 256)          # head_dim 64
+    act = "gelu_tanh" if causal else "relu"
+    params = O.make_params(cfg, 29, stress=True, bf16=True)
+    for B, T in ((3, 77), (2, 130), (1, 257), (2, 330)):
+        ids = O.make_prompt(cfg, 29 + T, B, T)
+        monkeypatch.delenv("RG_B200_PREFILL", raising=False)
+        a = model_for(backend, cfg, params, causal=causal, act=act, dtype="bf16", max_batch=B)
+        la = a.forward(ids.astype(np.float32))
+        monkeypatch.setenv("RG_B200_PREFILL", "simt")
+        b = model_for(backend, cfg, params, causal=causal, act=act, dtype="bf16", max_batch=B)
+        lb = b.forward(ids.astype(np.float32))
+        monkeypatch.delenv("RG_B200_PREFILL", raising=False)
+        want = O.forward(params, cfg, ids, causal=causal, act=act)
+        scale = np.abs(want).max(-1, keepdims=True)
+        assert (np.abs(lb - want) / scale).max() <= BF16_REL_TOL
+        assert (np.abs(la - want) / scale).max() <= BF16_REL_TOL
+        assert np.isfinite(la).all()
+        # launch counts tell that the tensor-core attention ran: one more kernel per block (the Q / V^T preparation)
+        l0 = backend.launch_count
+        a.forward(ids.astype(np.float32))
+        n_tc = backend.launch_count - l0
+        l0 = backend.launch_count
+        b.forward(ids.astype(np.float32))
+        assert n_tc != backend.launch_count - l0
