@@ -47,10 +47,7 @@ __device__ __forceinline__ float rg_vec_in_value(const rg_vec_in& in, int B, int
     if (in.kind == RG_IN_REDUCE) {
         float v = in.base ? in.base[(size_t)b * K + k] : 0.f;
         if (in.bias) v += in.bias[k];
-        const float* p = in.parts + (size_t)b * K + k;
-        const size_t stride = (size_t)B * K;
-        for (int s = 0; s < in.nparts; s++) v += p[s * stride];
-        return v;
+        return v + rg_sum_parts(in.parts + (size_t)b * K + k, in.nparts, (size_t)B * K);
     } else {
         const int h = k / in.hd, d = k - h * in.hd;
         const int rec = in.hd + 2;
@@ -275,9 +272,7 @@ __global__ void __launch_bounds__(128) rg_attn_step_kernel(rg_attn_step_args p) 
         if (which > 0 && !owns_new) continue;
         const int col = which * p.D + h * HD + d;
         float v = p.qkv_bias ? p.qkv_bias[col] : 0.f;
-        const float* pp = p.qkv_parts + (size_t)b * 3 * p.D + col;
-        const size_t stride = (size_t)p.B * 3 * p.D;
-        for (int k = 0; k < p.nparts; k++) v += pp[k * stride];
+        v += rg_sum_parts(p.qkv_parts + (size_t)b * 3 * p.D + col, p.nparts, (size_t)p.B * 3 * p.D);
         if (which == 0) sq[d] = v;
         else if (which == 1) sk[d] = v;
         else sv[d] = v;

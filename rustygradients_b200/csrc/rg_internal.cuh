@@ -147,6 +147,26 @@ __device__ __forceinline__ float rg_apply_act(float x, int act) {
     return act == RG_ACT_RELU ? fmaxf(x, 0.f) : rg_gelu_tanh(x);
 }
 
+// Sum of the k-split partials of one element, in index order, with 8 loads in flight at a time (a chain of dependent
+// load-add steps would cost one memory latency per partial).
+__device__ __forceinline__ float rg_sum_parts(const float* __restrict__ p, int nparts, size_t pstride) {
+    float t = 0.f;
+    int z = 0;
+    for (; z + 8 <= nparts; z += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = p[(size_t)(z + u) * pstride];
+#pragma unroll
+        for (int u = 0; u < 8; u++) t += v[u];
+    }
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) v[u] = (z + u < nparts) ? p[(size_t)(z + u) * pstride] : 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; u++) t += v[u];
+    return t;
+}
+
 __device__ __forceinline__ float rg_to_float(float v) { return v; }
 __device__ __forceinline__ float rg_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -38,7 +38,7 @@ static __global__ void __launch_bounds__(256) rg_rows_res_ln_bf16_kernel(const f
         if (k < D) {
             float t = x[row * D + k];
             if (bias) t += bias[k];
-            for (int z = 0; z < nparts; z++) t += parts[(size_t)z * pstride + row * D + k];
+            t += rg_sum_parts(parts + row * D + k, nparts, pstride);
             if (store_x) x[row * D + k] = t;
             v[i] = t;
             s += t;
@@ -66,7 +66,7 @@ static __global__ void rg_rows_act_bf16_kernel(const float* __restrict__ parts, 
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     float v = bias ? bias[i % N] : 0.f;
-    for (int z = 0; z < nparts; z++) v += parts[(size_t)z * pstride + i];
+    v += rg_sum_parts(parts + i, nparts, pstride);
     if (act >= 0) v = rg_apply_act(v, act);
     out16[i] = __float2bfloat16_rn(v);
 }
