@@ -209,6 +209,7 @@ template <typename WT>
 __global__ void rg_embed_step_kernel(const uint32_t* __restrict__ tokens, int C, const WT* __restrict__ wte,
                                      const WT* __restrict__ wpe, int D, long long ldt, float* __restrict__ x,
                                      const int* __restrict__ pos_next, int* __restrict__ pos) {
+    rg_pdl_sync();
     const int t = *pos_next;
     const int b = blockIdx.x;
     if (b == 0 && threadIdx.x == 0) *pos = t;
@@ -243,6 +244,7 @@ struct rg_attn_step_args {
 
 template <typename KT, int HD>
 __global__ void __launch_bounds__(128) rg_attn_step_kernel(rg_attn_step_args p) {
+    rg_pdl_sync();
     constexpr int VEC = 16 / sizeof(KT);  // elements per 16-byte load
     constexpr int LPR = HD / VEC;         // lanes per cached row
     constexpr int RPW = 32 / LPR;         // rows per warp per load
@@ -375,6 +377,7 @@ struct rg_pick_args {
 };
 
 static __global__ void __launch_bounds__(1024) rg_pick_kernel(rg_pick_args p) {
+    rg_pdl_sync();
     __shared__ float bv[32];
     __shared__ int bi[32];
     const int b = blockIdx.x, tid = threadIdx.x;
@@ -411,6 +414,7 @@ static __global__ void __launch_bounds__(1024) rg_pick_kernel(rg_pick_args p) {
 // out[b][h*hd + d] = sum_s w_s o_s[d] / sum_s w_s l_s with w_s = exp(m_s - max m).
 static __global__ void rg_attn_merge_kernel(const float* __restrict__ ap, float* __restrict__ out, int B, int H, int hd, int NS,
                                             __nv_bfloat16* __restrict__ out16 = nullptr) {
+    rg_pdl_sync();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= B * H * hd) return;
     rg_vec_in in;

@@ -75,6 +75,7 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
 rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const tc_epi e) {
+    rg_pdl_sync();
     extern __shared__ unsigned char tc_smem_raw[];
     // 1024-byte aligned tiles (the swizzle pattern is a function of the address)
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -371,7 +372,7 @@ static rg_status tc_gemm(rg_ctx* ctx, const void* A16, int M, int K, const void*
         e.C = ctx->tc_ws, e.ldc = N, e.bias = nullptr, e.res = nullptr, e.act = -1;
     }
     dim3 grid(std::min(ntiles, ctx->sm_count), 1, splits);  // persistent: one CTA per SM walks the tiles
-    rg_gemm_tc_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(tmA, tmB, e);
+    RG_CUDA(rg_launch(ctx->pdl, rg_gemm_tc_kernel, grid, dim3(TC_THREADS), TC_SMEM_BYTES, ctx->stream, tmA, tmB, e));
     RG_CUDA(cudaGetLastError());
     RG_LAUNCHED(ctx);
     if (splits > 1 && !raw) {

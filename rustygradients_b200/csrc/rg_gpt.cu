@@ -1048,9 +1048,19 @@ static int enqueue_step_rows_tc(rg_gpt* m, int B) {
     const uint64_t l0 = m->ctx->launches;
     const int D = m->D, F = m->F, act = m->cfg.activation;
     __nv_bfloat16* a16 = (__nv_bfloat16*)m->pa16;
-    rg_embed_step_kernel<__nv_bfloat16><<<B, 128, 0, s>>>(m->tokens, m->C, (const __nv_bfloat16*)m->wte, (const __nv_bfloat16*)m->wpe,
-                                                          D, m->ldt, m->px, m->d_pos_next, m->d_pos);
-    rg_rows_res_ln_bf16_kernel<<<B, 256, 0, s>>>(nullptr, 0, 0, nullptr, m->px, 0, m->layers[0].ln1g, m->layers[0].ln1b, a16, D);
+    // every kernel of the step starts with rg_pdl_sync(): launched with programmatic stream serialization, the launch
+    // latency of a kernel overlaps the execution of the one before it (RG_B200_PDL=0 turns the attribute off)
+    const char* pdl_env = getenv("RG_B200_PDL");
+    const bool pdl = !(pdl_env && strcmp(pdl_env, "0") == 0);
+    struct pdl_scope {
+        rg_ctx* c;
+        pdl_scope(rg_ctx* ctx, bool on) : c(ctx) { c->pdl = on; }
+        ~pdl_scope() { c->pdl = false; }
+    } scope(m->ctx, pdl);
+    rg_launch(pdl, rg_embed_step_kernel<__nv_bfloat16>, dim3(B), dim3(128), 0, s, m->tokens, m->C, (const __nv_bfloat16*)m->wte,
+              (const __nv_bfloat16*)m->wpe, D, m->ldt, m->px, m->d_pos_next, m->d_pos);
+    rg_launch(pdl, rg_rows_res_ln_bf16_kernel, dim3(B), dim3(256), 0, s, nullptr, 0, (size_t)0, nullptr, m->px, 0, m->layers[0].ln1g,
+              m->layers[0].ln1b, a16, D);
     m->ctx->launches += 2;
     // context slices per (sequence, head): enough CTAs to fill the GPU a few times over, no more
     const int NS = std::max(1, std::min(m->NS, rg_cdiv(4 * m->ctx->sm_count, B * m->Hl)));
@@ -1067,23 +1077,25 @@ static int enqueue_step_rows_tc(rg_gpt* m, int B) {
             a.B = B, a.H = m->Hl, a.C = m->C, a.D = m->Dl, a.NS = NS;
             a.scale = 1.f / sqrtf((float)m->hd);
             dim3 grid(NS, m->Hl, B);
-            if (m->hd == 32) rg_attn_step_kernel<__nv_bfloat16, 32><<<grid, 128, 0, s>>>(a);
-            else if (m->hd == 64) rg_attn_step_kernel<__nv_bfloat16, 64><<<grid, 128, 0, s>>>(a);
-            else rg_attn_step_kernel<__nv_bfloat16, 128><<<grid, 128, 0, s>>>(a);
-            rg_attn_merge_kernel<<<rg_cdiv(B * D, 256), 256, 0, s>>>(m->ap, nullptr, B, m->Hl, m->hd, NS, a16);
+            if (m->hd == 32) rg_launch(pdl, rg_attn_step_kernel<__nv_bfloat16, 32>, grid, dim3(128), 0, s, a);
+            else if (m->hd == 64) rg_launch(pdl, rg_attn_step_kernel<__nv_bfloat16, 64>, grid, dim3(128), 0, s, a);
+            else rg_launch(pdl, rg_attn_step_kernel<__nv_bfloat16, 128>, grid, dim3(128), 0, s, a);
+            rg_launch(pdl, rg_attn_merge_kernel, dim3(rg_cdiv(B * D, 256)), dim3(256), 0, s, (const float*)m->ap, (float*)nullptr, B,
+                      m->Hl, m->hd, NS, a16);
             m->ctx->launches += 2;
         }
         if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, D, y.o.Wt, D, &parts, &np) != RG_OK) return -1;
-        rg_rows_res_ln_bf16_kernel<<<B, 256, 0, s>>>(parts, np, (size_t)B * D, y.o.b, m->px, 1, y.ln2g, y.ln2b, a16, D);
+        rg_launch(pdl, rg_rows_res_ln_bf16_kernel, dim3(B), dim3(256), 0, s, parts, np, (size_t)B * D, (const float*)y.o.b, m->px, 1,
+                  (const float*)y.ln2g, (const float*)y.ln2b, a16, D);
         RG_LAUNCHED(m->ctx);
         if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, D, y.fc1.Wt, F, &parts, &np) != RG_OK) return -1;
-        rg_rows_act_bf16_kernel<<<rg_cdiv((long long)B * F, 256), 256, 0, s>>>(parts, np, (size_t)B * F, y.fc1.b, F, (size_t)B * F, act,
-                                                                           a16);
+        rg_launch(pdl, rg_rows_act_bf16_kernel, dim3(rg_cdiv((long long)B * F, 256)), dim3(256), 0, s, parts, np, (size_t)B * F,
+                  (const float*)y.fc1.b, F, (size_t)B * F, act, a16);
         RG_LAUNCHED(m->ctx);
         if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, F, y.fc2.Wt, D, &parts, &np) != RG_OK) return -1;
         const bool last = l + 1 == m->L;
-        rg_rows_res_ln_bf16_kernel<<<B, 256, 0, s>>>(parts, np, (size_t)B * D, y.fc2.b, m->px, 1, last ? m->lnfg : m->layers[l + 1].ln1g,
-                                                      last ? m->lnfb : m->layers[l + 1].ln1b, a16, D);
+        rg_launch(pdl, rg_rows_res_ln_bf16_kernel, dim3(B), dim3(256), 0, s, parts, np, (size_t)B * D, (const float*)y.fc2.b, m->px, 1,
+                  (const float*)(last ? m->lnfg : m->layers[l + 1].ln1g), (const float*)(last ? m->lnfb : m->layers[l + 1].ln1b), a16, D);
         RG_LAUNCHED(m->ctx);
     }
     if (rg_gemm_bf16_tc(m->ctx, a16, B, D, m->head.Wt, m->V, m->logits, m->V, m->head.b, nullptr, 0, -1) != RG_OK) return -1;
@@ -1091,7 +1103,7 @@ static int enqueue_step_rows_tc(rg_gpt* m, int B) {
     pa.parts = m->logits, pa.nparts = 1, pa.bias = nullptr, pa.logits = m->logits;
     pa.tokens = m->tokens, pa.picks = m->picks, pa.pos = m->d_pos, pa.pos_next = m->d_pos_next;
     pa.B = B, pa.V = m->V, pa.C = m->C;
-    rg_pick_kernel<<<B, 1024, 0, s>>>(pa);
+    rg_launch(pdl, rg_pick_kernel, dim3(B), dim3(1024), 0, s, pa);
     RG_LAUNCHED(m->ctx);
     const int n = (int)(m->ctx->launches - l0);
     m->ctx->launches = l0;

@@ -8,7 +8,9 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <cstring>
 #include <memory>
+#include <utility>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -46,6 +48,7 @@ struct rg_ctx {
     uint64_t launches = 0;
     int* d_flag = nullptr;  // device word kernels raise on invalid input
     int* h_flag = nullptr;  // pinned mirror
+    bool pdl = false;        // launch with programmatic stream serialization (inside a chain of rg_pdl_sync kernels)
     float* tc_ws = nullptr;  // split-k workspace of the tensor-core GEMM (this context's stream only)
     size_t tc_ws_bytes = 0;
 };
@@ -78,6 +81,22 @@ struct rg_ctx_guard {
 };
 
 #define RG_LAUNCHED(ctx) ((ctx)->launches++)
+
+#ifdef __CUDACC__
+// Kernel launch that, when pdl is set, may begin before the previous kernel of the stream has finished (the kernel
+// must call rg_pdl_sync() first thing).
+template <typename... P, typename... A>
+static inline cudaError_t rg_launch(bool pdl, void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, A&&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at, cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, P(std::forward<A>(args))...);
+}
+#endif
 
 static inline int rg_cdiv(long long a, long long b) { return (int)((a + b - 1) / b); }
 
@@ -165,6 +184,15 @@ __device__ __forceinline__ float rg_sum_parts(const float* __restrict__ p, int n
 #pragma unroll
     for (int u = 0; u < 8; u++) t += v[u];
     return t;
+}
+
+// Programmatic dependent launch: a kernel launched with the "programmatic stream serialization" attribute may start
+// while its predecessor is still running; this call (first statement of every kernel of such a chain) lets this
+// kernel's own successor be scheduled early and then waits until the predecessor has completed and its memory is
+// visible.  Without the attribute both instructions return at once.
+__device__ __forceinline__ void rg_pdl_sync() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 __device__ __forceinline__ float rg_to_float(float v) { return v; }

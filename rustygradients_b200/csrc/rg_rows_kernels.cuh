@@ -27,6 +27,7 @@ static __global__ void __launch_bounds__(256) rg_rows_res_ln_bf16_kernel(const f
                                                                          int store_x, const float* __restrict__ gamma,
                                                                          const float* __restrict__ beta,
                                                                          __nv_bfloat16* __restrict__ out16, int D) {
+    rg_pdl_sync();
     __shared__ float sm8[8];
     const size_t row = blockIdx.x;
     float v[RG_ROWS_MAX_D / 256];
@@ -63,6 +64,7 @@ static __global__ void __launch_bounds__(256) rg_rows_res_ln_bf16_kernel(const f
 static __global__ void rg_rows_act_bf16_kernel(const float* __restrict__ parts, int nparts, size_t pstride,
                                                const float* __restrict__ bias, int N, size_t total, int act,
                                                __nv_bfloat16* __restrict__ out16) {
+    rg_pdl_sync();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     float v = bias ? bias[i % N] : 0.f;
