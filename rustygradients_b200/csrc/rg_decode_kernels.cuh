@@ -101,6 +101,7 @@ struct rg_wvec<__nv_bfloat16> {
 // ---------------------------------------------------------------------------
 template <typename WT, int BT>
 __global__ void __launch_bounds__(256) rg_gemv_kernel(rg_gemv_args p) {
+    rg_pdl_sync();
     constexpr int VEC = rg_wvec<WT>::N;
     constexpr int NT = 32 * VEC;
     extern __shared__ float smem[];

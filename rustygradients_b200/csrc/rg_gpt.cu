@@ -819,7 +819,7 @@ static void launch_gemv_bt(rg_gpt* m, const rg_gemv_args& a) {
     dim3 grid(rg_cdiv(a.N, NT), a.ksplit, rg_cdiv(a.B, BT));
     const int xlen = a.in.post == RG_POST_LN ? a.K : a.krows;
     const size_t smem = (size_t)BT * xlen * 4;
-    rg_gemv_kernel<WT, BT><<<grid, 256, smem, m->ctx->stream>>>(a);
+    rg_launch(m->ctx->pdl, rg_gemv_kernel<WT, BT>, grid, dim3(256), smem, m->ctx->stream, a);
 }
 template <typename WT>
 static void launch_gemv_wt(rg_gpt* m, const rg_gemv_args& a) {
@@ -861,9 +861,10 @@ static void launch_attn_step(rg_gpt* m, int l, int B) {
     a.scale = 1.f / sqrtf((float)m->hd);
     dim3 grid(m->NS, m->Hl, B);
     cudaStream_t s = m->ctx->stream;
-    if (m->hd == 32) rg_attn_step_kernel<KT, 32><<<grid, 128, 0, s>>>(a);
-    else if (m->hd == 64) rg_attn_step_kernel<KT, 64><<<grid, 128, 0, s>>>(a);
-    else rg_attn_step_kernel<KT, 128><<<grid, 128, 0, s>>>(a);
+    const bool pdl = m->ctx->pdl;
+    if (m->hd == 32) rg_launch(pdl, rg_attn_step_kernel<KT, 32>, grid, dim3(128), 0, s, a);
+    else if (m->hd == 64) rg_launch(pdl, rg_attn_step_kernel<KT, 64>, grid, dim3(128), 0, s, a);
+    else rg_launch(pdl, rg_attn_step_kernel<KT, 128>, grid, dim3(128), 0, s, a);
 }
 
 // Enqueue the kernels of one token step for B sequences; returns how many.
@@ -893,9 +894,21 @@ static rg_linear tp_reduce(rg_gpt* m, const rg_linear& lin, int B, int* n, int s
 }
 
 // Enqueue the kernels of one token step for B sequences; returns how many.
+// While alive, projection / attention kernels of this context are launched with programmatic stream serialization
+// (they all begin with rg_pdl_sync()); RG_B200_PDL=0 turns it off.
+struct rg_pdl_scope {
+    rg_ctx* c;
+    explicit rg_pdl_scope(rg_ctx* ctx) : c(ctx) {
+        const char* e = getenv("RG_B200_PDL");
+        c->pdl = !(e && strcmp(e, "0") == 0);
+    }
+    ~rg_pdl_scope() { c->pdl = false; }
+};
+
 static int enqueue_step(rg_gpt* m, int B) {
     cudaStream_t s = m->ctx->stream;
     int n = 0;
+    rg_pdl_scope pdl_scope(m->ctx);
     if (m->tp_fused) {
         rg_bump_kernel<<<1, 1, 0, s>>>(m->d_tp_epoch);  // every rank runs the same steps: the tags agree
         n++;
@@ -1050,13 +1063,8 @@ static int enqueue_step_rows_tc(rg_gpt* m, int B) {
     __nv_bfloat16* a16 = (__nv_bfloat16*)m->pa16;
     // every kernel of the step starts with rg_pdl_sync(): launched with programmatic stream serialization, the launch
     // latency of a kernel overlaps the execution of the one before it (RG_B200_PDL=0 turns the attribute off)
-    const char* pdl_env = getenv("RG_B200_PDL");
-    const bool pdl = !(pdl_env && strcmp(pdl_env, "0") == 0);
-    struct pdl_scope {
-        rg_ctx* c;
-        pdl_scope(rg_ctx* ctx, bool on) : c(ctx) { c->pdl = on; }
-        ~pdl_scope() { c->pdl = false; }
-    } scope(m->ctx, pdl);
+    rg_pdl_scope scope(m->ctx);
+    const bool pdl = m->ctx->pdl;
     rg_launch(pdl, rg_embed_step_kernel<__nv_bfloat16>, dim3(B), dim3(128), 0, s, m->tokens, m->C, (const __nv_bfloat16*)m->wte,
               (const __nv_bfloat16*)m->wpe, D, m->ldt, m->px, m->d_pos_next, m->d_pos);
     rg_launch(pdl, rg_rows_res_ln_bf16_kernel, dim3(B), dim3(256), 0, s, nullptr, 0, (size_t)0, nullptr, m->px, 0, m->layers[0].ln1g,
