@@ -45,12 +45,14 @@ def _rank(rank, world, port, q, allreduce):
     be = rg.B200Backend(rank)
     results = {}
     for name, cfg, dtype, B in (("f32", O.GptConfig(48, 301, 2, 3, 96), "f32", 2),
-                                ("bf16", O.GptConfig(48, 1000, 2, 5, 320), "bf16", 3)):
+                                ("bf16", O.GptConfig(48, 1000, 2, 5, 320), "bf16", 3),
+                                # 9 sequences: the GEMM form of the token step with its row-split all-reduces
+                                ("bf16_rows", O.GptConfig(48, 1000, 2, 5, 320), "bf16", 9)):
         params = O.make_params(cfg, 31, stress=True, bf16=(dtype == "bf16"))
         prompt = O.make_prompt(cfg, 31, B, 10)
         toks, want = O.generate_causal(params, cfg, prompt, 12)
         m = rg.GPTModel(be, rg.GptConfig(cfg.block_size, cfg.vocab_size, cfg.num_layers, cfg.num_heads, cfg.embedding_dim,
-                                         weight_dtype=dtype, max_batch=4, tp_rank=rank, tp_size=world))
+                                         weight_dtype=dtype, max_batch=max(4, B), tp_rank=rank, tp_size=world))
         m.load_parameters(params)
         ident = [rg.GPTModel.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ident, src=0)
@@ -90,7 +92,7 @@ def test_tensor_parallel_two_gpus(allreduce):
     [p.start() for p in procs]
     res = dict(q.get(timeout=600) for _ in range(2))
     [p.join(60) for p in procs]
-    for name in ("f32", "bf16"):
+    for name in ("f32", "bf16", "bf16_rows"):
         a, b = res[0][name], res[1][name]
         assert a[4] == b[4]                                   # both ranks generate the same ids
         for maxabs, rel, ferr, picks_ok, _, f32_tol, bf16_tol, fused in (a, b):
