@@ -34,7 +34,7 @@ WORKLOAD = "gpt2-small-shape vocab1024 f32 batch1 prompt128 decode256"
 CFG_INDEX = 1
 NOMINAL_HBM_GBS = 8000.0     # the figure the metric's roofline is defined on
 FALLBACK_HBM_GBS = 6650.0
-NCU_TRAFFIC_RATIO = 1.0022   # measured DRAM bytes / algorithmic bytes, profiles/token_loop_kernel_*
+NCU_TRAFFIC_RATIO = 1.0036   # measured DRAM bytes (read + write) / algorithmic bytes, profiles/token_loop_kernel_*
 
 
 def measured_hbm_peak():
@@ -286,7 +286,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                          "peak_kind": peak_kind, "bytes_per_launch": step_bytes * G,
                          "bytes_per_token": step_bytes, "launch_ms": ms / args.steps,
                          "frac_of_8TBs_nominal": achieved / NOMINAL_HBM_GBS,
-                         # dram__bytes_read+write of one ncu capture of the same kernel on 8 tokens (353.9 MB per token
+                         # dram__bytes_read+write of one ncu capture of the same kernel on 8 tokens (354.4 MB per token
                          # against 353.1 MB algorithmic at that context), scaled to this launch by the tokens it runs
                          "traffic": step_bytes * G * NCU_TRAFFIC_RATIO if launches <= 2 * args.steps else None},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": int(B * P * 4),
