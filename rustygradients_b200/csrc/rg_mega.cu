@@ -669,9 +669,9 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
         for (int oi = 0; oi < nops; oi++) {
             const mg_op op = ops[oi];
             // A barrier at the start of an op is only needed when shared memory of the previous op could still be in
-            // use: attention scratch (either side), or a further group of the same stage (the `red` array).  Between
-            // two projection stages the barrier after the previous dot products already ordered everything.
-            if (op.type == MG_ATTN || prev_type == MG_ATTN || !(op.flags & MG_FIRST)) {
+            // use: attention scratch (either side).  Between two projection ops (of one stage or of two) the barrier
+            // after the previous dot products already ordered everything, and the partial-sum arrays alternate.
+            if (op.type == MG_ATTN || prev_type == MG_ATTN) {
                 if (mg_csync_or(ctl.dead)) ctl.dead = true;
             }
             if (ctl.dead) break;
