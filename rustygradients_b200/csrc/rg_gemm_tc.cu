@@ -12,7 +12,7 @@
 //    accumulate) with shared-memory matrix descriptors; two accumulators live in TMEM
 //    (128 lanes x 128 columns each), so the epilogue of a tile overlaps the MMAs of the next;
 //  * tcgen05.commit signals "stage consumed" and "accumulator complete" on mbarriers;
-//  * four epilogue warps read the accumulator back with tcgen05.ld (32 lanes x 32
+//  * eight epilogue warps read the accumulator back with tcgen05.ld (32 lanes x 32
 //    columns at a time) and apply bias / activation / residual on the way to HBM.
 // No cluster multicast anywhere.  Every wait is bounded: on expiry the CTA raises an
 // error word, still frees its TMEM and returns.
@@ -26,7 +26,7 @@
 #define TC_BN 128
 #define TC_BK 64
 #define TC_STAGES 6
-#define TC_THREADS 192
+#define TC_THREADS 320  // TMA warp, MMA warp, 8 epilogue warps
 #define TC_SPIN_LIMIT (1u << 22)
 #define TC_STAGE_BYTES ((TC_BM + TC_BN) * TC_BK * 2)
 #define TC_SMEM_BYTES (TC_STAGES * TC_STAGE_BYTES + 1024 + 256)
@@ -98,7 +98,7 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         for (int b = 0; b < 2; b++) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&acc_full[b])) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(tc_smem(&acc_empty[b])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;" ::"r"(tc_smem(&acc_empty[b])) : "memory");
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -186,8 +186,11 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
         }
     } else {
-        // ===== epilogue warps 2..5: TMEM lane quarter = warp % 4 =====
+        // ===== epilogue warps 2..9: TMEM lane quarter = warp % 4; warps 2..5 take the left half of the columns,
+        // warps 6..9 the right half (the epilogue, not the MMA, bounds a tile when K is short: with 4 warps a 128x128
+        // tile of the out-projection took ~20 us to drain) =====
         const int q = warp & 3;
+        const int c_begin = warp < 6 ? 0 : TC_BN / 64, c_end = c_begin + TC_BN / 64;
         uint32_t tl = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, tl++) {
@@ -198,7 +201,7 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int m = m0 + q * 32 + lane;
 #pragma unroll 1
-            for (int c = 0; c < TC_BN / 32; c++) {
+            for (int c = c_begin; c < c_end; c++) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + buf * TC_BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32);
                 asm volatile(
@@ -212,7 +215,7 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (c == TC_BN / 32 - 1) {
+                if (c == c_end - 1) {
                     // every column of this accumulator has been read: hand it back before the last stores
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
