@@ -343,7 +343,7 @@ static rg_status tc_gemm(rg_ctx* ctx, const void* A16, int M, int K, const void*
     RG_TRY(tc_make_map(&tmB, Wt16, N, K));
     const int nkb = K / TC_BK, ntiles = rg_cdiv(N, TC_BN) * rg_cdiv(M, TC_BM);
     int splits = 1;
-    if (M <= TC_BM && ntiles < ctx->sm_count / 2) splits = std::max(1, std::min(nkb / 2, ctx->sm_count / ntiles));
+    if (M <= TC_BM && ntiles < ctx->sm_count / 2) splits = std::max(1, std::min(nkb / 3, ctx->sm_count / ntiles));  // at least 3 k-blocks per CTA (A/B: 2 and 4 are slower)
     const int kb_per = rg_cdiv(nkb, splits);
     splits = rg_cdiv(nkb, kb_per);
     tc_epi e;
