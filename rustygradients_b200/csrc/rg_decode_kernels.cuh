@@ -386,12 +386,29 @@ static __global__ void __launch_bounds__(1024) rg_pick_kernel(rg_pick_args p) {
     float best = -INFINITY;
     int besti = 0x7fffffff;
     const size_t stride = (size_t)p.B * p.V;
-    for (int v = tid; v < p.V; v += blockDim.x) {
-        float x = p.bias ? p.bias[v] : 0.f;
-        const float* pp = p.parts + (size_t)b * p.V + v;
-        for (int s = 0; s < p.nparts; s++) x += pp[s * stride];
-        p.logits[(size_t)b * p.V + v] = x;
-        if (x > best) best = x, besti = v;  // strided ascending: first hit is the lowest index of this thread
+    // finished logits in place (one part, no bias): nothing to add and nothing to store, only the scan
+    const bool in_place = p.nparts == 1 && !p.bias && p.parts == p.logits;
+    // 4 elements per thread and trip, their loads issued together (a load -> compare chain per element would cost one
+    // memory latency each: V / 1024 = 49 of them for the full vocabulary)
+    for (int v0 = tid; v0 < p.V; v0 += 4 * blockDim.x) {
+        float x[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int v = v0 + u * blockDim.x;
+            x[u] = -INFINITY;
+            if (v < p.V) {
+                const float* pp = p.parts + (size_t)b * p.V + v;
+                x[u] = in_place ? pp[0] : (p.bias ? p.bias[v] : 0.f) + rg_sum_parts(pp, p.nparts, stride);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int v = v0 + u * blockDim.x;
+            if (v < p.V) {
+                if (!in_place) p.logits[(size_t)b * p.V + v] = x[u];
+                if (x[u] > best) best = x[u], besti = v;  // ascending per thread: the first hit is its lowest index
+            }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
