@@ -12,6 +12,12 @@ One "step" is one decode run: the 256 token-loop iterations that follow a
 public generate() call with host buffers (prompt upload, prompt pass, decode,
 ids download).  With N > 1 (under torchrun) every rank runs its own sequence on
 its own GPU: sequences are the shard, there is no collective in the loop.
+
+Two more records ride in the same JSON line (skipped with --no-extra):
+  "batched": the GPT-2-small shape with the full vocabulary and bf16 weights, prompt 256, decode 256, 64 sequences
+             in total split over the N ranks (strong scaling) and 64 sequences on every rank (weak scaling);
+  "tp":      (N >= 2) the GPT-2-XL shape, bf16, prompt 512, decode 256, tensor parallel over the N ranks with the
+             peer-memory all-reduce, batch 1 and batch 32, bytes counted PER GPU.
 Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
@@ -167,11 +173,109 @@ def run_reference(args, rank: int) -> None:
     line = {"impl": "reference", "metric": "decode tokens/sec (GPT-2-small shape)", "value": v, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "kv_cache": False},
+            "config": {"workload": WORKLOAD, "kv_cache": False, "causal": False, "activation": "relu"},
             "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
             "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------
+# the sharded batch and the tensor-parallel model (records inside the main line)
+# --------------------------------------------------------------------------
+def _timed_decode(torch, model, be, stream, barrier, P, G, runs):
+    """ms per decode run of G steps from position P (device time, this rank); one untimed run first."""
+    model.rewind(P)
+    model.decode_run(G)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(runs):
+        model.rewind(P)
+        model.decode_run(G)
+    e1.record(stream)
+    be.synchronize()
+    barrier()
+    return e0.elapsed_time(e1) / runs
+
+
+def _sum_over_ranks(torch, value, world, dev):
+    if world == 1:
+        return int(value)
+    import torch.distributed as dist
+    t = torch.tensor([int(value)], dtype=torch.int64, device=dev)
+    dist.all_reduce(t)
+    return int(t.item())
+
+
+def run_batched(torch, rg, O, be, dev, stream, barrier, rank, world):
+    """Configuration 2 of the oracle's list: vocabulary 50257, bf16 weights, prompt 256, decode 256; 64 sequences."""
+    from rustygradients_b200.sharding import max_over_ranks, shard_range
+    c = O.CONFIGS[2]
+    cfg, P, G, TOTAL = c["cfg"], c["prompt"], c["gen"], 64
+    seed = O.config_seed(2)
+    params = O.make_params(cfg, seed)                 # f32 draws; the engine rounds them to bf16 (RNE) at load
+    model = rg.GPTModel(be, rg.GptConfig(cfg.block_size, cfg.vocab_size, cfg.num_layers, cfg.num_heads, cfg.embedding_dim,
+                                         weight_dtype="bf16", max_batch=TOTAL))
+    model.load_parameters(params)
+    peak, _ = measured_hbm_peak()
+    mean_ctx = P + (G - 1) / 2.0 + 1.0
+    rec = {"workload": f"gpt2-small-shape vocab50257 bf16 prompt{P} decode{G}, {TOTAL} sequences", "kv_cache": "bf16"}
+    prompts = O.make_prompt(cfg, seed, TOTAL * world, P)
+    legs = [("strong", shard_range(TOTAL, rank, world))]
+    if world > 1:
+        legs.append(("weak", (rank * TOTAL, (rank + 1) * TOTAL)))
+    for name, (lo, hi) in legs:
+        B = hi - lo
+        model.prefill(np.ascontiguousarray(prompts[lo:hi]), want_logits=False)
+        ms = max_over_ranks(_timed_decode(torch, model, be, stream, barrier, P, G, 3), world, dev)
+        ids = model.read_tokens(P + 1, G - 1, B)
+        n_seq = TOTAL if name == "strong" else TOTAL * world
+        step_bytes = model.decode_step_bytes(B, mean_ctx)         # this GPU, one token step
+        gbs = step_bytes / (ms * 1e-3 / G) / 1e9
+        rec[name] = {"sequences_total": n_seq, "sequences_per_gpu": B, "tokens_per_s": n_seq * G / (ms * 1e-3),
+                     "us_per_step": ms * 1e3 / G, "bytes_per_step_per_gpu": step_bytes, "gb_per_s_per_gpu": gbs,
+                     "frac_of_measured_peak": gbs / peak, "frac_of_8TBs_nominal": gbs / NOMINAL_HBM_GBS,
+                     "ids_checksum": _sum_over_ranks(torch, np.asarray(ids, dtype=np.uint64).sum(), world, dev)}
+    if world == 1:
+        rec["weak"] = rec["strong"]
+    model.close()
+    return rec
+
+
+def run_tp(torch, rg, be, dev, stream, barrier, rank, world):
+    """GPT-2-XL shape (vocabulary 50257, d_model 1600, 48 layers, 25 heads), bf16, tensor parallel over all ranks."""
+    import torch.distributed as dist
+    from rustygradients_b200.sharding import max_over_ranks
+    V, D, L, H, P, G = 50257, 1600, 48, 25, 512, 256
+    peak, _ = measured_hbm_peak()
+    model = rg.GPTModel(be, rg.GptConfig(1024, V, L, H, D, weight_dtype="bf16", max_batch=32, tp_rank=rank, tp_size=world))
+    prng = np.random.Generator(np.random.PCG64(20245))
+    params = [(prng.standard_normal(s, dtype=np.float32) * np.float32(0.02)) if s[0] != 1 or s[1] == V
+              else np.ones(s, np.float32) for s in model.parameter_shapes()]
+    model.load_parameters(params)                      # every rank keeps its shard of the same full list
+    del params
+    ident = torch.zeros(128, dtype=torch.uint8, device=dev)
+    if rank == 0:
+        ident = torch.tensor(list(rg.GPTModel.tp_unique_id()), dtype=torch.uint8, device=dev)
+    dist.broadcast(ident, src=0)
+    model.tp_init(bytes(ident.cpu().tolist()))
+    rec = {"workload": f"gpt2-xl-shape vocab{V} bf16 prompt{P} decode{G}", "tp_size": world,
+           "allreduce": "peer-memory kernel" if model.tp_fused() else "nccl"}
+    rng = np.random.Generator(np.random.PCG64(20246))
+    for B in (1, 32):
+        prompt = rng.integers(0, V, size=(B, P), dtype=np.uint32)
+        model.prefill(prompt, want_logits=False)
+        ms = max_over_ranks(_timed_decode(torch, model, be, stream, barrier, P, G, 2), world, dev)
+        ids = model.read_tokens(P + 1, G - 1, B)
+        step_bytes = model.decode_step_bytes(B, P + (G - 1) / 2.0 + 1.0)     # per GPU: the sharded terms divided by tp_size
+        gbs = step_bytes / (ms * 1e-3 / G) / 1e9
+        rec[f"batch{B}"] = {"tokens_per_s": B * G / (ms * 1e-3), "us_per_step": ms * 1e3 / G,
+                            "bytes_per_step_per_gpu": step_bytes, "gb_per_s_per_gpu": gbs,
+                            "frac_of_measured_peak": gbs / peak, "frac_of_8TBs_nominal": gbs / NOMINAL_HBM_GBS,
+                            "ids_checksum": int(np.asarray(ids, dtype=np.uint64).sum())}
+    model.close()
+    return rec
 
 
 # --------------------------------------------------------------------------
@@ -240,6 +344,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     ms = max_over_ranks(ev0.elapsed_time(ev1), world, dev)
     clocks = sampler.stop(t_wall0, t_wall1)
     ids_dev = model.read_tokens(P + 1, G - 1, B)       # picks of steps 0..G-2 (the last has no slot to keep)
+    step_bytes_main = model.decode_step_bytes(B, P + (G - 1) / 2.0 + 1.0)
 
     # ---- end to end through the public generate(): host prompt in, host ids out
     pin_prompt = torch.from_numpy(prompt.astype(np.int64)).to(torch.int32).pin_memory()
@@ -259,13 +364,19 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     assert np.array_equal(ids_e2e[:, 1:], ids_dev), "generate() and the device-resident loop disagree"
     assert int(first_pick[0, 0]) == int(ids_e2e[0, 0])
     all_ids = gather_ids(ids_e2e, world * B, rank, world, dev)   # once, after the loop: the only exchange
+    model.close()
+    extra = {}
+    if not args.no_extra:
+        extra["batched"] = run_batched(torch, rg, O, be, dev, stream, barrier, rank, world)
+        if world > 1:
+            extra["tp"] = run_tp(torch, rg, be, dev, stream, barrier, rank, world)
 
     if rank == 0:
         tokens = world * B * G * args.steps
         value = tokens / (ms * 1e-3)
         e2e_value = world * B * G * n_e2e / (ms_e2e * 1e-3)
         mean_ctx = P + (G - 1) / 2.0 + 1.0              # keys visible to a step, averaged over the run
-        step_bytes = model.decode_step_bytes(B, mean_ctx)   # one GPU, one token step
+        step_bytes = step_bytes_main                        # one GPU, one token step
         t_step = ms * 1e-3 / (args.steps * G)               # seconds per token step (slowest rank)
         achieved = step_bytes / t_step / 1e9
         peak, peak_kind = measured_hbm_peak()
@@ -274,7 +385,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD if G == c["gen"] else WORKLOAD + f" (SHORTENED to {G} tokens: not a bench value)",
-                       "sequences_per_gpu": B, "tokens_per_step": G, "kv_cache": "f32",
+                       "sequences_per_gpu": B, "tokens_per_step": G, "kv_cache": "f32", "causal": True,
+                       "activation": "gelu_tanh",
                        "l2": "inputs larger than L2 (343 MB of weights streamed per token vs 126 MB L2)",
                        "parallelism": f"{world} independent sequence shard(s), no collective in the loop"},
             "us_per_token": t_step * 1e6,
@@ -288,23 +400,124 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                          "frac_of_8TBs_nominal": achieved / NOMINAL_HBM_GBS,
                          # dram__bytes_read+write of one ncu capture of the same kernel on 8 tokens (354.4 MB per token
                          # against 353.1 MB algorithmic at that context), scaled to this launch by the tokens it runs
-                         "traffic": step_bytes * G * NCU_TRAFFIC_RATIO if launches <= 2 * args.steps else None},
+                         "traffic": step_bytes * G * NCU_TRAFFIC_RATIO if launches <= 2 * args.steps else None,
+                         "traffic_source": "not measured in this run: algorithmic bytes x 1.0036, the DRAM read+write ratio of "
+                                           "the ncu capture in profiles/token_loop_kernel_gpt2small_ncu_full.md"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": int(B * P * 4),
                     "d2h_bytes_per_step": int(B * G * 4), "calls": n_e2e,
                     "what": "generate(prompt, 256): pinned host ids -> device, prompt pass, 255 cached steps, ids -> host"},
             "gpu_launches": int(launches), "clocks": clocks,
             "ids_checksum": int(np.asarray(all_ids, dtype=np.uint64).sum()),
         }
+        line.update(extra)
         if world == 1 and not args.no_cpu_baseline:
             v, dt = cpu_reference_tokens_per_s(24, params)
             line["cpu_baseline"] = {
-                "value": v, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port",
+                "value": v, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port", "causal": False,
+                "activation": "relu", "kv_cache": False,
                 "sample": f"24 loop iterations at context lengths spread over 128..383 ({dt:.1f} s): the reference's loop "
                           "(full re-forward per id, no KV cache, unmasked attention, ReLU, all logit rows) in numpy f32 + OpenBLAS"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------
+# single small workloads for profiler captures: python bench.py --only decode|prefill|ingest [...]
+# (not the benchmark: they print their own JSON line and leave the contract line alone)
+# --------------------------------------------------------------------------
+def _random_params(model, vocab, seed):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    return [(rng.standard_normal(s, dtype=np.float32) * np.float32(0.02)) if s[0] != 1 or s[1] == vocab
+            else np.ones(s, np.float32) for s in model.parameter_shapes()]
+
+
+def run_only(a) -> None:
+    import torch
+    import rustygradients_b200 as rg
+    be = rg.B200Backend(0)
+    stream = torch.cuda.ExternalStream(be.stream, device=torch.device("cuda", 0))
+    rng = np.random.Generator(np.random.PCG64(9))
+    D, H, L, V = a.d_model, a.heads, a.layers, a.vocab
+    if a.only == "decode":
+        # token-step time of `batch` sequences: batches 1, 2, 4 run in the persistent kernel, larger ones as separate launches
+        m = rg.GPTModel(be, rg.GptConfig(1024, V, L, H, D, weight_dtype=a.dtype, max_batch=a.batch))
+        m.load_parameters(_random_params(m, V, 9))
+        prompt = rng.integers(0, V, size=(a.batch, a.prompt), dtype=np.uint32)
+        m.prefill(prompt, want_logits=False)
+        m.decode_run(min(a.iters, 40))
+        times = []
+        for _ in range(3):
+            m.rewind(a.prompt)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            m.decode_run(a.iters)
+            e1.record(stream)
+            be.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3 / a.iters)
+        us = min(times)
+        by = m.decode_step_bytes(a.batch, a.prompt + a.iters / 2)
+        print(json.dumps({"only": "decode", "batch": a.batch, "dtype": a.dtype, "prompt": a.prompt, "steps": a.iters,
+                          "us_per_step": us, "tokens_per_s": a.batch / (us * 1e-6),
+                          "algorithmic_gb_per_s": by / (us * 1e-6) / 1e9, "launches": be.launch_count}))
+    elif a.only == "prefill":
+        # prompt pass of `batch` prompts (the tensor-core part of the path); RG_B200_PREFILL=simt times the CUDA-core GEMM
+        m = rg.GPTModel(be, rg.GptConfig(1024, V, L, H, D, weight_dtype=a.dtype, max_batch=a.batch))
+        m.load_parameters(_random_params(m, V, 7))
+        ids = rng.integers(0, V, size=(a.batch, a.prompt), dtype=np.uint32)
+        m.prefill(ids, want_logits=False)
+        be.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(a.iters):
+            m.prefill(ids, want_logits=False)
+        be.synchronize()
+        dt = (time.perf_counter() - t0) / a.iters
+        rows = a.batch * a.prompt
+        flops = 2.0 * rows * L * 12 * D * D + 2.0 * a.batch * D * V + 4.0 * L * a.batch * a.prompt * a.prompt * D / 2
+        print(json.dumps({"only": "prefill", "prompt_pass_ms": dt * 1e3, "tflops": flops / dt / 1e12, "rows": rows, "layers": L,
+                          "gemm": os.environ.get("RG_B200_PREFILL", "tcgen05"), "launches": be.launch_count}))
+    else:
+        # time from a safetensors file on disk (page cache) to a model that is ready to generate
+        from rustygradients_b200 import serialization as S
+        C = 1024
+
+        def n(*shape):
+            return rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02)
+
+        t = {}
+        m = rg.GPTModel(be, rg.GptConfig(C, V, L, H, D))
+        if a.names == "hf_gpt2":
+            t["wte.weight"], t["wpe.weight"] = n(V, D), n(C, D)
+            for l in range(L):
+                h = f"h.{l}."
+                t[h + "attn.c_attn.weight"], t[h + "attn.c_attn.bias"] = n(D, 3 * D), n(3 * D)
+                t[h + "attn.c_proj.weight"], t[h + "attn.c_proj.bias"] = n(D, D), n(D)
+                t[h + "mlp.c_fc.weight"], t[h + "mlp.c_fc.bias"] = n(D, 4 * D), n(4 * D)
+                t[h + "mlp.c_proj.weight"], t[h + "mlp.c_proj.bias"] = n(4 * D, D), n(D)
+                for ln in ("ln_1", "ln_2"):
+                    t[h + ln + ".weight"], t[h + ln + ".bias"] = np.ones(D, np.float32), np.zeros(D, np.float32)
+            t["ln_f.weight"], t["ln_f.bias"] = np.ones(D, np.float32), np.zeros(D, np.float32)
+        else:
+            for name, shp in zip(S.rusty_names(L), m.parameter_shapes()):
+                t[name] = n(*shp)
+        path = os.path.join("/tmp", f"rg_ingest_bench_{os.getpid()}.safetensors")
+        S.write_safetensors(path, t)
+        size = os.path.getsize(path)
+        del t
+        try:
+            times = []
+            for _ in range(3):
+                be.synchronize()
+                t0 = time.perf_counter()
+                m.load_safetensors(path, names=a.names)
+                be.synchronize()
+                times.append(time.perf_counter() - t0)
+            ids = m.generate(np.zeros((1, 4), np.uint32), 4)
+            print(json.dumps({"only": "ingest", "file_bytes": size, "names": a.names, "load_s": times,
+                              "best_gb_per_s": size / min(times) / 1e9, "generated": [int(x) for x in np.asarray(ids).ravel()]}))
+        finally:
+            os.remove(path)
 
 
 def main() -> None:
@@ -314,9 +527,24 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the batched and tensor-parallel records")
     ap.add_argument("--tokens-per-step", type=int, default=0,
                     help="shorten the decode run (profiling only; the default is the workload's 256)")
+    ap.add_argument("--only", choices=["decode", "prefill", "ingest"],
+                    help="run one small workload for a profiler capture instead of the benchmark")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=12)
+    ap.add_argument("--iters", type=int, default=3, help="--only: timed repetitions (decode: token steps)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--vocab", type=int, default=50257)
+    ap.add_argument("--d-model", type=int, default=768)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--names", default="hf_gpt2", choices=["hf_gpt2", "rusty"])
     args = ap.parse_args()
+    if args.only:
+        run_only(args)
+        return
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -173,8 +173,9 @@ RG_API rg_status rg_gpt_read_tokens(rg_gpt* m, size_t from, size_t n, uint32_t* 
 RG_API size_t rg_gpt_position(const rg_gpt* m);
 /* Forget the cached context (start of a new generate call). */
 RG_API rg_status rg_gpt_reset(rg_gpt* m);
-/* Algorithmic bytes one decode step reads at context length T for B sequences
- * (weights + biases + LN + one table row pair + K/V of every cached position). */
+/* Algorithmic bytes one decode step reads ON THIS GPU at context length T for B sequences
+ * (weights + biases + LN + one table row pair + K/V of every cached position; with tensor
+ * parallelism the shard of this rank plus the replicated LayerNorm / bias terms). */
 RG_API double rg_gpt_decode_step_bytes(const rg_gpt* m, size_t B, double mean_ctx);
 
 /* Tensor parallelism (nothing to mirror: the reference has no multi-device path).  With
@@ -201,6 +202,18 @@ RG_API int rg_gpt_tp_fused(const rg_gpt* m);
 RG_API rg_status rg_gpt_trace_enable(rg_gpt* m, int on);
 RG_API rg_status rg_gpt_trace_read(rg_gpt* m, uint64_t* out, size_t cap_rows, size_t* n_rows);
 
+/* Test hook, no counterpart in the reference: makes the failure paths of the bounded device waits reachable without
+ * a device fault.  what = 1 (ctx): raise the flag word that a tensor-core kernel's wait raises when it gives up, so
+ * that the next synchronising call reports RG_ERR_TIMEOUT.  what = 2 (m): the persistent cluster kernel's head
+ * cluster 0 withholds its partial vector of block `value` (-1: off), so every wait that depends on it runs out.
+ * what = 3 (m): iteration limit of that kernel's waits (>= 1000).  what = 4 (m): form of the token loop (0 default,
+ * 1 cluster kernel, 2 persistent kernel, 3 separate launches).  what = 5 (m): iteration limit of the persistent
+ * kernel's waits (0: built-in).  what = 6 (m): CTA 0 of the persistent kernel withholds its q|k|v outputs of block
+ * `value` (-1: off).  what = 7 (ctx): runs the tensor-parallel all-reduce kernel as rank 0 of 2 on this GPU with a
+ * limit of `value` polls while nothing plays rank 1, and reports the RG_ERR_TIMEOUT that a missing peer produces.
+ * The unused handle may be NULL. */
+RG_API rg_status rg_debug_hook(rg_ctx* ctx, rg_gpt* m, int what, long long value);
+
 /* ---- allocation-free projection ------------------------------------------- */
 /* No counterpart in the reference.  y[N] = x[K] . W[K,N] + bias[N] (bias may be NULL)
  * for a caller that cannot allocate device memory (inside a capture/replay region,
@@ -209,7 +222,8 @@ RG_API rg_status rg_gpt_trace_read(rg_gpt* m, uint64_t* out, size_t cap_rows, si
  * 16-byte aligned with N a multiple of 4.  The split-k partial sums live in a fixed
  * 2 MiB array inside the library image (held by every GPU that loads the library
  * until exit), which limits N to 16384 and K to 32768; larger sizes return
- * RG_ERR_INVALID_INPUT.  Runs on the current device, on `stream` (a cudaStream_t).
+ * RG_ERR_INVALID_INPUT.  Runs on the current device, on `stream` (a cudaStream_t that
+ * belongs to the current device: the scratch address used is that device's).
  * The first call on each device also looks up the array's address: make that
  * call before any stream capture begins.  All calls share the array, so calls that
  * overlap on the GPU race; nothing in it needs clearing between calls.  Never calls

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "librg_b200.so")
-SOURCES = ["rg_api.cu", "rg_gpt.cu", "rg_mega.cu", "rg_gemm_tc.cu", "rg_attn_tc.cu", "rg_noalloc.cu", "rg_ingest.cu",
+SOURCES = ["rg_api.cu", "rg_gpt.cu", "rg_mega.cu", "rg_cloop.cu", "rg_gemm_tc.cu", "rg_attn_tc.cu", "rg_noalloc.cu", "rg_ingest.cu",
            "rg_tokenizer.cu"]
 
 

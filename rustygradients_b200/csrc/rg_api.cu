@@ -86,11 +86,23 @@ extern "C" rg_status rg_ctx_destroy(rg_ctx* ctx) {
     return RG_OK;
 }
 
+// The bounded waits of the tensor-core GEMM and attention kernels raise the second flag word when they give up (tiles or
+// split-k partials are then missing).  Called after a stream synchronise: reports it once and clears the word.
+rg_status rg_tc_wait_check(rg_ctx* ctx) {
+    int v = 0;
+    RG_CUDA(cudaMemcpy(&v, ctx->d_flag + 1, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v) {
+        RG_CUDA(cudaMemset(ctx->d_flag + 1, 0, sizeof(int)));
+        return rg_fail(RG_ERR_TIMEOUT, "a bounded wait inside a tensor-core kernel gave up; its output is incomplete");
+    }
+    return RG_OK;
+}
+
 extern "C" rg_status rg_synchronize(rg_ctx* ctx) {
     if (!ctx) return rg_fail(RG_ERR_INVALID_INPUT, "rg_synchronize: ctx is NULL");
     rg_ctx_guard g(ctx);
     RG_CUDA(cudaStreamSynchronize(ctx->stream));
-    return RG_OK;
+    return rg_tc_wait_check(ctx);
 }
 
 extern "C" void* rg_ctx_stream(rg_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
@@ -179,7 +191,7 @@ extern "C" rg_status rg_to_vec(rg_ctx* ctx, const rg_storage* st, float* outp, s
     rg_ctx_guard g(ctx);
     if (st->len) RG_CUDA(cudaMemcpyAsync(outp, st->data(), st->len * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     RG_CUDA(cudaStreamSynchronize(ctx->stream));
-    return RG_OK;
+    return rg_tc_wait_check(ctx);
 }
 
 extern "C" rg_status rg_shape(const rg_storage* st, size_t* shape_out, int cap, int* ndim_out) {

@@ -89,6 +89,7 @@ struct rg_tp_ar_args {
     const unsigned* epoch;
     int site, nsites;
     int* err;
+    unsigned limit;  // polls after which a wait gives up
 };
 static __global__ void __launch_bounds__(256) rg_tp_allreduce_kernel(rg_tp_ar_args a) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -117,7 +118,7 @@ static __global__ void __launch_bounds__(256) rg_tp_allreduce_kernel(rg_tp_ar_ar
                 vals[r] = __uint_as_float((unsigned)w[r]);
                 pending &= ~(1u << r);
             }
-        if (pending && (++spins > RG_TP_SPIN_LIMIT || ((spins & 1023u) == 0 && *(volatile int*)a.err))) {
+        if (pending && (++spins > a.limit || ((spins & 1023u) == 0 && *(volatile int*)a.err))) {
             *a.err = 1;
             break;
         }
@@ -397,6 +398,7 @@ extern "C" rg_status rg_gpt_destroy(rg_gpt* m) {
     tp_peer_close(m);
     if (m->nccl_comm && g_nccl.ok) g_nccl.CommDestroy((ncclComm_t)m->nccl_comm);
     rg_mega_destroy(m);
+    rg_cloop_destroy(m);
     for (void* p : m->allocs) cudaFree(p);
     delete m;
     return RG_OK;
@@ -533,7 +535,8 @@ extern "C" rg_status rg_gpt_load_params(rg_gpt* m, const float* const* data, con
     m->loaded = true;
     m->pos = 0;
     m->curB = 0;
-    return rg_mega_create(m);
+    RG_TRY(rg_mega_create(m));
+    return rg_cloop_create(m);
 }
 
 // ---------------------------------------------------------------------------
@@ -777,7 +780,7 @@ extern "C" rg_status rg_gpt_forward(rg_gpt* m, const float* idx_f32, size_t B, s
     RG_CUDA(cudaMemcpyAsync(logits, m->plogits, need * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
     RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
     m->pos = 0, m->curB = 0;  // the cache now holds this call's keys, not a generation context
-    return RG_OK;
+    return rg_tc_wait_check(m->ctx);
 }
 
 static rg_status set_pos(rg_gpt* m, size_t T) {
@@ -798,7 +801,10 @@ static rg_status prefill_locked(rg_gpt* m, const uint32_t* ids, size_t B, size_t
     if (logits_last)
         RG_CUDA(cudaMemcpyAsync(logits_last, m->logits, B * (size_t)m->V * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
     if (argmax) RG_CUDA(cudaMemcpyAsync(argmax, m->picks, B * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
-    if (logits_last || argmax) RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    if (logits_last || argmax) {
+        RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
+        return rg_tc_wait_check(m->ctx);
+    }
     return RG_OK;
 }
 
@@ -880,7 +886,7 @@ static rg_linear tp_reduce(rg_gpt* m, const rg_linear& lin, int B, int* n, int s
         a.parts = lin.parts, a.nparts = lin.ksplit, a.cnt = cnt, a.out = m->tp_vec;
         for (int p = 0; p < m->tp_size; p++) a.peer[p] = m->tp_peer[p];
         a.T = m->tp_size, a.rank = m->tp_rank, a.slot = (size_t)m->Bmax * m->D;
-        a.epoch = m->d_tp_epoch, a.site = site, a.nsites = 2 * m->L, a.err = m->d_tp_err;
+        a.epoch = m->d_tp_epoch, a.site = site, a.nsites = 2 * m->L, a.err = m->d_tp_err, a.limit = RG_TP_SPIN_LIMIT;
         rg_tp_allreduce_kernel<<<rg_cdiv((long long)cnt, 256), 256, 0, m->ctx->stream>>>(a);
         *n += 1;
     } else {
@@ -1118,9 +1124,30 @@ static int enqueue_step_rows_tc(rg_gpt* m, int B) {
     return n;
 }
 
+static rg_status tp_check(rg_gpt* m);
+// After a synchronise: has any bounded device wait given up (tensor-parallel all-reduce, the persistent token-loop
+// kernels, the tensor-core kernels of the prompt pass and of the batched step)?
+static rg_status waits_check(rg_gpt* m) {
+    RG_TRY(tp_check(m));
+    RG_TRY(rg_mega_check(m));
+    RG_TRY(rg_cloop_check(m));
+    return rg_tc_wait_check(m->ctx);
+}
+
 static rg_status run_steps(rg_gpt* m, size_t steps) {
     const int B = (int)m->curB;
     cudaStream_t s = m->ctx->stream;
+    if (rg_cloop_supports(m, B)) {
+        // one persistent kernel of thread-block clusters runs all the steps
+        rg_status st = rg_cloop_run(m, B, m->pos, steps);
+        if (st == RG_OK) {
+            m->pos += steps;
+            return RG_OK;
+        }
+        if (st != RG_ERR_UNSUPPORTED) return st;
+        // no cluster shape of this GPU fits the model, or the clusters cannot all be resident: the forms below
+        // compute the same thing
+    }
     if (rg_mega_supports(m, B)) {
         // one persistent cooperative kernel runs all the steps
         rg_status st = rg_mega_run(m, B, m->pos, steps);
@@ -1155,6 +1182,8 @@ static rg_status run_steps(rg_gpt* m, size_t steps) {
             m->kernels_per_step =
                 rows_path ? (rows_fused ? enqueue_step_rows_tc(m, B) : enqueue_step_rows(m, B)) : enqueue_step(m, B);
             cudaError_t e = cudaStreamEndCapture(s, &gr);
+            const cudaError_t le = cudaGetLastError();  // a launch that was rejected while capturing leaves its error here
+            if (e == cudaSuccess && le != cudaSuccess) e = le;
             if (m->kernels_per_step < 0) {
                 if (gr) cudaGraphDestroy(gr);
                 return RG_ERR_BACKEND;
@@ -1185,8 +1214,7 @@ extern "C" rg_status rg_gpt_decode_step(rg_gpt* m, const uint32_t* tok, float* l
     if (logits) RG_CUDA(cudaMemcpyAsync(logits, m->logits, B * (size_t)m->V * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
     if (argmax) RG_CUDA(cudaMemcpyAsync(argmax, m->picks, B * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
     RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
-    RG_TRY(tp_check(m));
-    return rg_mega_check(m);
+    return waits_check(m);
 }
 
 extern "C" rg_status rg_gpt_decode_run(rg_gpt* m, size_t n_steps) {
@@ -1220,8 +1248,7 @@ extern "C" rg_status rg_gpt_read_tokens(rg_gpt* m, size_t from, size_t n, uint32
         RG_CUDA(cudaMemcpy2DAsync(out, n * 4, m->tokens + from, (size_t)m->C * 4, n * 4, m->curB, cudaMemcpyDeviceToHost,
                                   m->ctx->stream));
     RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
-    RG_TRY(tp_check(m));
-    return rg_mega_check(m);
+    return waits_check(m);
 }
 
 extern "C" size_t rg_gpt_position(const rg_gpt* m) { return m ? m->pos : 0; }
@@ -1286,8 +1313,7 @@ extern "C" rg_status rg_gpt_generate(rg_gpt* m, const uint32_t* prompt, size_t B
                                       m->ctx->stream));
         }
         RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
-        RG_TRY(tp_check(m));
-    return rg_mega_check(m);
+        return waits_check(m);
     }
     // The reference's loop proper (no mask, so no cache): every new id re-runs the
     // whole window of the last block_size ids (wasm_api.rs:102-118).
@@ -1315,10 +1341,13 @@ extern "C" rg_status rg_gpt_generate(rg_gpt* m, const uint32_t* prompt, size_t B
 
 extern "C" double rg_gpt_decode_step_bytes(const rg_gpt* m, size_t B, double mean_ctx) {
     if (!m) return 0.0;
-    const double D = m->D, V = m->V, L = m->L;
-    const double w = L * (12.0 * D * D + 13.0 * D) + D * V + V + 4.0 * D;
+    // per GPU: with tensor parallelism the projections, their split biases and the cache are this rank's shard; LayerNorm
+    // parameters, the biases added after an all-reduce and the two embedding rows are read by every rank
+    const double D = m->D, L = m->L, Dl = m->Dl, Fl = m->Fl, Vl = m->Vl;
+    const double layer = (D * 3.0 * Dl + 3.0 * Dl) + (Dl * D + D) + (D * Fl + Fl) + (Fl * D + D) + 4.0 * D;
+    const double w = L * layer + D * Vl + Vl + 4.0 * D;
     const double kv = m->bf16 ? 2.0 : 4.0;
-    return (double)m->wsize * w + (double)B * kv * 2.0 * L * D * mean_ctx;
+    return (double)m->wsize * w + (double)B * kv * 2.0 * L * Dl * mean_ctx;
 }
 
 extern "C" rg_status rg_gpt_tp_unique_id(uint8_t id_out[128]) {
@@ -1424,5 +1453,71 @@ extern "C" rg_status rg_gpt_trace_enable(rg_gpt* m, int on) {
 extern "C" rg_status rg_gpt_trace_read(rg_gpt* m, uint64_t* out, size_t cap_rows, size_t* n_rows) {
     if (!m || !out || !n_rows) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
     rg_ctx_guard g(m->ctx);
+    if (rg_cloop_active(m)) return rg_cloop_trace(m, (unsigned long long*)out, cap_rows, n_rows);
     return rg_mega_trace(m, (unsigned long long*)out, cap_rows, n_rows);
+}
+
+// Test hook (see rg_b200.h): makes the failure paths of the bounded device waits reachable without a device fault.
+extern "C" rg_status rg_debug_hook(rg_ctx* ctx, rg_gpt* m, int what, long long value) {
+    switch (what) {
+        case 1: {  // raise the flag word of the tensor-core kernels' waits, as a wait that gave up would
+            if (!ctx) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+            rg_ctx_guard g(ctx);
+            const int one = 1;
+            RG_CUDA(cudaMemcpy(ctx->d_flag + 1, &one, sizeof(int), cudaMemcpyHostToDevice));
+            return RG_OK;
+        }
+        case 2:  // cluster token loop: head cluster 0 withholds its out-projection partial of layer `value` (-1: off)
+            if (!m) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+            rg_cloop_debug(m, (int)value, 0);
+            return RG_OK;
+        case 3:  // cluster token loop: iteration limit of every wait
+            if (!m || value < 1000) return rg_fail(RG_ERR_INVALID_INPUT, "the limit must be at least 1000");
+            rg_cloop_debug(m, m->cloop ? -2 : -1, (unsigned)value);
+            return RG_OK;
+        case 4:  // form of the token loop: 0 the default, 1 the cluster kernel, 2 the persistent kernel, 3 separate launches
+            if (!m || value < 0 || value > 3) return rg_fail(RG_ERR_INVALID_INPUT, "form 0..3");
+            m->use_cloop = value == 1 && m->cloop != nullptr;
+            m->use_mega = (value == 0 || value == 2) && m->mega != nullptr;
+            return RG_OK;
+        case 5:  // persistent kernel: iteration limit of every wait (0: the built-in limit)
+            if (!m || value < 0) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+            rg_mega_debug(m, (unsigned)value, -3);
+            return RG_OK;
+        case 6:  // persistent kernel: CTA 0 withholds its q|k|v outputs of block `value` (-1: off)
+            if (!m) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+            rg_mega_debug(m, 0xffffffffu, (int)value);
+            return RG_OK;
+        case 7: {  // the tensor-parallel all-reduce kernel as rank 0 of 2 on one GPU; rank 1 never contributes: the wait must run out
+            if (!ctx || value < 1000) return rg_fail(RG_ERR_INVALID_INPUT, "needs a context and a limit of at least 1000 polls");
+            rg_ctx_guard g(ctx);
+            const size_t cnt = 768;
+            float *parts = nullptr, *out = nullptr;
+            unsigned long long* recv = nullptr;
+            unsigned* ep = nullptr;
+            RG_CUDA(cudaMalloc(&parts, cnt * 4));
+            RG_CUDA(cudaMalloc(&out, cnt * 4));
+            RG_CUDA(cudaMalloc(&recv, 2 * 2 * 2 * cnt * 8));  // two receive buffers of [2 parities][2 ranks][cnt]
+            RG_CUDA(cudaMalloc(&ep, 16));
+            RG_CUDA(cudaMemset(parts, 0, cnt * 4));
+            RG_CUDA(cudaMemset(recv, 0, 2 * 2 * 2 * cnt * 8));
+            RG_CUDA(cudaMemset(ep, 0, 16));
+            rg_tp_ar_args a;
+            memset(&a, 0, sizeof(a));
+            a.parts = parts, a.nparts = 1, a.cnt = cnt, a.out = out, a.T = 2, a.rank = 0, a.slot = cnt;
+            a.peer[0] = recv, a.peer[1] = recv + 2 * 2 * cnt;
+            a.epoch = ep, a.site = 0, a.nsites = 1, a.err = reinterpret_cast<int*>(ep + 2), a.limit = (unsigned)value;
+            rg_tp_allreduce_kernel<<<rg_cdiv((long long)cnt, 256), 256, 0, ctx->stream>>>(a);
+            RG_LAUNCHED(ctx);
+            int err = 0;
+            cudaError_t e = cudaStreamSynchronize(ctx->stream);
+            if (e == cudaSuccess) e = cudaMemcpy(&err, a.err, 4, cudaMemcpyDeviceToHost);
+            cudaFree(parts), cudaFree(out), cudaFree(recv), cudaFree(ep);
+            RG_CUDA(e);
+            if (err) return rg_fail(RG_ERR_TIMEOUT, "tensor-parallel all-reduce: a peer's contribution did not arrive in time");
+            return RG_OK;
+        }
+        default:
+            return rg_fail(RG_ERR_INVALID_INPUT, "unknown hook %d", what);
+    }
 }

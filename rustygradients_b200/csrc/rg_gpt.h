@@ -2,7 +2,8 @@
 #pragma once
 #include "rg_internal.cuh"
 
-struct rg_mega;  // persistent token-loop kernel state (rg_mega.cu)
+struct rg_mega;   // persistent token-loop kernel state (rg_mega.cu)
+struct rg_cloop;  // persistent token-loop kernel of thread-block clusters (rg_cloop.cu)
 
 struct rg_linear {
     void* W = nullptr;  // [K][ldw] f32 or bf16
@@ -76,6 +77,9 @@ struct rg_gpt {
     // persistent token-loop kernel (null when the model shape is outside its limits)
     rg_mega* mega = nullptr;
     bool use_mega = true;
+    // the same loop as a kernel of thread-block clusters (tried first; null or unusable -> the kernel above)
+    rg_cloop* cloop = nullptr;
+    bool use_cloop = true;
     bool trace_on = false;
     uint32_t epoch = 0;  // token steps run so far by the persistent kernel (tags of its exchange buffers)
 };
@@ -97,5 +101,18 @@ void rg_mega_destroy(rg_gpt* m);
 bool rg_mega_supports(const rg_gpt* m, int B);
 rg_status rg_mega_run(rg_gpt* m, int B, size_t pos0, size_t n_steps);  // enqueue n_steps token steps
 rg_status rg_mega_check(rg_gpt* m);
+// test hooks: spin_limit 0xffffffff and withhold_layer -3 keep the current values
+void rg_mega_debug(rg_gpt* m, unsigned spin_limit, int withhold_layer);
 rg_status rg_mega_trace(rg_gpt* m, unsigned long long* out, size_t cap_rows, size_t* n_rows);             // after a synchronise: did a bounded wait give up?
 
+
+// rg_cloop.cu: same contract as the rg_mega_* functions
+rg_status rg_cloop_create(rg_gpt* m);
+void rg_cloop_destroy(rg_gpt* m);
+bool rg_cloop_supports(const rg_gpt* m, int B);
+rg_status rg_cloop_run(rg_gpt* m, int B, size_t pos0, size_t n_steps);
+rg_status rg_cloop_check(rg_gpt* m);
+rg_status rg_cloop_trace(rg_gpt* m, unsigned long long* out, size_t cap_rows, size_t* n_rows);
+bool rg_cloop_active(const rg_gpt* m);
+// test hook: head cluster 0 withholds its partial of `withhold_layer` (-1: off); spin_limit 0 keeps the current limit
+void rg_cloop_debug(rg_gpt* m, int withhold_layer, unsigned spin_limit);

@@ -26,6 +26,8 @@
 #include <memory>
 
 #include "rg_gpt.h"
+
+#include <exception>
 #include "rg_json.h"
 
 namespace {
@@ -123,13 +125,17 @@ struct st_file {
             if (dt->str != "F32")  // the reference reader accepts nothing else (safetensors_format.rs:111-116)
                 return rg_fail(RG_ERR_SERIALIZATION, "%s: tensor `%s`: Expected F32 dtype, got %s", path, kv.first.c_str(), dt->str.c_str());
             host_tensor t;
+            uint64_t elems = 1;  // checked product: a crafted shape must not wrap around to a small byte count
             for (size_t i = 0; i < sh->count(); i++) {
                 uint64_t d = 0;
                 if (!sh->index_at(i, &d)) return rg_fail(RG_ERR_SERIALIZATION, "%s: bad shape of `%s`", path, kv.first.c_str());
+                if (d != 0 && elems > (uint64_t)avail / d)
+                    return rg_fail(RG_ERR_SERIALIZATION, "%s: shape of `%s` describes more data than the file holds", path, kv.first.c_str());
+                elems *= d;
                 t.shape.push_back((size_t)d);
             }
             uint64_t b = 0, en = 0;
-            if (!off->index_at(0, &b) || !off->index_at(1, &en) || en < b || en > avail || en - b != (uint64_t)t.count() * 4)
+            if (elems > (uint64_t)avail / 4 || !off->index_at(0, &b) || !off->index_at(1, &en) || en < b || en > avail || en - b != elems * 4)
                 return rg_fail(RG_ERR_SERIALIZATION, "%s: data_offsets of `%s` do not match its shape or the file", path, kv.first.c_str());
             if (((uintptr_t)(base + b)) & 3) {  // header length not a multiple of 4: floats cannot be read in place
                 copies.emplace_back(t.count());
@@ -307,56 +313,68 @@ rg_status load_slots(rg_gpt* m, const std::vector<slot>& s) {
 }  // namespace
 
 extern "C" rg_status rg_model_metadata_read(const char* path, rg_gpt_config* cfg) {
-    if (!path || !cfg) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
-    mapped_file f;
-    RG_TRY(f.open(path));
-    rg_json j;
-    RG_TRY(parse_json_file(f, path, &j));
-    const rg_json* meta = j.get("metadata");  // a JsonCheckpoint carries it one level down
-    return metadata_from_json(meta ? *meta : j, path, cfg);
+    try {
+        if (!path || !cfg) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+        mapped_file f;
+        RG_TRY(f.open(path));
+        rg_json j;
+        RG_TRY(parse_json_file(f, path, &j));
+        const rg_json* meta = j.get("metadata");  // a JsonCheckpoint carries it one level down
+        return metadata_from_json(meta ? *meta : j, path, cfg);
+    } catch (const std::exception& e) {
+        return rg_fail(RG_ERR_SERIALIZATION, "%s: %s", path ? path : "(null)", e.what());
+    }
 }
 
 extern "C" rg_status rg_gpt_load_safetensors(rg_gpt* m, const char* path, int names) {
-    if (!m || !path) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
-    if (names != RG_NAMES_AUTO && names != RG_NAMES_RUSTY && names != RG_NAMES_HF_GPT2)
-        return rg_fail(RG_ERR_INVALID_INPUT, "unknown naming scheme %d", names);
-    st_file f;
-    RG_TRY(f.open(path));
-    if (names == RG_NAMES_AUTO)
-        names = (f.find("wte.weight") || f.find("transformer.wte.weight")) ? RG_NAMES_HF_GPT2 : RG_NAMES_RUSTY;
-    std::vector<slot> s((size_t)rg_gpt_num_params(m));
-    assembler a(m, f, path);
-    RG_TRY(names == RG_NAMES_HF_GPT2 ? assemble_hf(m, a, s) : assemble_rusty(m, a, s));
-    return load_slots(m, s);
+    try {
+        if (!m || !path) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+        if (names != RG_NAMES_AUTO && names != RG_NAMES_RUSTY && names != RG_NAMES_HF_GPT2)
+            return rg_fail(RG_ERR_INVALID_INPUT, "unknown naming scheme %d", names);
+        st_file f;
+        RG_TRY(f.open(path));
+        if (names == RG_NAMES_AUTO)
+            names = (f.find("wte.weight") || f.find("transformer.wte.weight")) ? RG_NAMES_HF_GPT2 : RG_NAMES_RUSTY;
+        std::vector<slot> s((size_t)rg_gpt_num_params(m));
+        assembler a(m, f, path);
+        RG_TRY(names == RG_NAMES_HF_GPT2 ? assemble_hf(m, a, s) : assemble_rusty(m, a, s));
+        return load_slots(m, s);
+    } catch (const std::exception& e) {
+        return rg_fail(RG_ERR_SERIALIZATION, "%s: %s", path ? path : "(null)", e.what());
+    }
 }
 
 extern "C" rg_status rg_gpt_load_json(rg_gpt* m, const char* path) {
-    if (!m || !path) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
-    mapped_file f;
-    RG_TRY(f.open(path));
-    rg_json j;
-    RG_TRY(parse_json_file(f, path, &j));
-    const rg_json* w = j.t == rg_json::OBJ ? j.get("weights") : &j;
-    if (!w || w->t != rg_json::ARR) return rg_fail(RG_ERR_SERIALIZATION, "%s: expected an array of {shape, data}", path);
-    const int want = rg_gpt_num_params(m);
-    if ((int)w->arr.size() != want)
-        return rg_fail(RG_ERR_SHAPE, "Mismatch in number of parameter tensors during loading: got %zu, model has %d", w->arr.size(), want);
-    std::vector<slot> s((size_t)want);
-    for (int i = 0; i < want; i++) {
-        const rg_json* sh = w->arr[i].get("shape");
-        const rg_json* da = w->arr[i].get("data");
-        if (!sh || !sh->is_number_array() || !da || !da->is_number_array())
-            return rg_fail(RG_ERR_SERIALIZATION, "%s: tensor %d lacks `shape` or `data`", path, i);
-        size_t want_shape[2];
-        rg_gpt_param_shape(m, i, want_shape);
-        uint64_t d0 = 0, d1 = 0;
-        if (sh->count() != 2 || !sh->index_at(0, &d0) || !sh->index_at(1, &d1) || d0 != want_shape[0] || d1 != want_shape[1])
-            return rg_fail(RG_ERR_SHAPE, "Mismatch in tensor shape during loading: parameter %d expected [%zu, %zu]", i, want_shape[0],
-                           want_shape[1]);
-        if (da->count() != d0 * d1)  // Array::from_shape_vec fails there (src/wasm_api.rs:193-194)
-            return rg_fail(RG_ERR_SHAPE, "%s: tensor %d holds %zu values for shape [%llu, %llu]", path, i, da->count(),
-                           (unsigned long long)d0, (unsigned long long)d1);
-        s[i].data = da->nums.data(), s[i].shape[0] = (size_t)d0, s[i].shape[1] = (size_t)d1;
+    try {
+        if (!m || !path) return rg_fail(RG_ERR_INVALID_INPUT, "NULL argument");
+        mapped_file f;
+        RG_TRY(f.open(path));
+        rg_json j;
+        RG_TRY(parse_json_file(f, path, &j));
+        const rg_json* w = j.t == rg_json::OBJ ? j.get("weights") : &j;
+        if (!w || w->t != rg_json::ARR) return rg_fail(RG_ERR_SERIALIZATION, "%s: expected an array of {shape, data}", path);
+        const int want = rg_gpt_num_params(m);
+        if ((int)w->arr.size() != want)
+            return rg_fail(RG_ERR_SHAPE, "Mismatch in number of parameter tensors during loading: got %zu, model has %d", w->arr.size(), want);
+        std::vector<slot> s((size_t)want);
+        for (int i = 0; i < want; i++) {
+            const rg_json* sh = w->arr[i].get("shape");
+            const rg_json* da = w->arr[i].get("data");
+            if (!sh || !sh->is_number_array() || !da || !da->is_number_array())
+                return rg_fail(RG_ERR_SERIALIZATION, "%s: tensor %d lacks `shape` or `data`", path, i);
+            size_t want_shape[2];
+            rg_gpt_param_shape(m, i, want_shape);
+            uint64_t d0 = 0, d1 = 0;
+            if (sh->count() != 2 || !sh->index_at(0, &d0) || !sh->index_at(1, &d1) || d0 != want_shape[0] || d1 != want_shape[1])
+                return rg_fail(RG_ERR_SHAPE, "Mismatch in tensor shape during loading: parameter %d expected [%zu, %zu]", i, want_shape[0],
+                               want_shape[1]);
+            if (da->count() != d0 * d1)  // Array::from_shape_vec fails there (src/wasm_api.rs:193-194)
+                return rg_fail(RG_ERR_SHAPE, "%s: tensor %d holds %zu values for shape [%llu, %llu]", path, i, da->count(),
+                               (unsigned long long)d0, (unsigned long long)d1);
+            s[i].data = da->nums.data(), s[i].shape[0] = (size_t)d0, s[i].shape[1] = (size_t)d1;
+        }
+        return load_slots(m, s);
+    } catch (const std::exception& e) {
+        return rg_fail(RG_ERR_SERIALIZATION, "%s: %s", path ? path : "(null)", e.what());
     }
-    return load_slots(m, s);
 }

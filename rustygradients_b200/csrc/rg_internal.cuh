@@ -70,6 +70,7 @@ struct rg_storage {
 };
 
 rg_status rg_alloc_storage(rg_ctx* ctx, const size_t* shape, int ndim, rg_storage** out);
+rg_status rg_tc_wait_check(rg_ctx* ctx);  // after a synchronise: did a wait of a tensor-core kernel give up?
 
 struct rg_ctx_guard {
     rg_ctx* c;

@@ -30,16 +30,12 @@
 
 #include <algorithm>
 
-#define MG_THREADS 256
-#define MG_SLOT_BYTES 32768
-#define MG_ATTN_PASSES (MG_SLOT_BYTES / 4096)  // rows of a full K/V chunk that one lane group of one warp handles
-#define MG_SPIN_LIMIT (1u << 21)
-#define MG_BMAX 4
+#include "rg_loop_dev.cuh"
+
 
 enum { MG_QKV = 0, MG_ATTN = 1, MG_OPROJ = 2, MG_FC1 = 3, MG_FC2 = 4, MG_HEAD = 5 };
 enum { MG_FIRST = 1, MG_LAST = 2 };
 
-typedef unsigned long long mg_word;  // (tag << 32) | payload bits
 
 struct mg_op {
     int type, layer;
@@ -81,6 +77,8 @@ struct mg_params {
     uint32_t epoch0;
     int nslot, max_ops, max_cd, res_cap, n_pick_ctas;
     int poll_sleep;
+    uint32_t spin_limit;  // iterations after which a wait gives up
+    int withhold_layer;   // test hook: CTA 0 does not publish its q|k|v outputs of this block (-1: off)
     int S;  // CTAs that share one (sequence, head) in the attention stage, each a slice of the context
     float scale;
 };
@@ -110,137 +108,11 @@ struct rg_mega {
     int built_for_B = 0;
     int place[6] = {0, 0, 0, 0, 0, 0};  // chosen position of every exchange vector inside its region
     bool placed = false;                // ... once mg_place_exchange has run
+    uint32_t spin_limit = MG_SPIN_LIMIT;
+    int withhold_layer = -1;
     std::vector<void*> allocs;
 };
 
-// ---------------------------------------------------------------------------
-// device helpers
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t mg_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mg_mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mg_smem(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mg_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mg_smem(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mg_mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(mg_smem(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void mg_bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(mg_smem(dst)),
-                 "l"(src), "r"(bytes), "r"(mg_smem(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void mg_fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
-__device__ __forceinline__ mg_word mg_ld_word(const mg_word* p) {
-    mg_word v;
-    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void mg_st_word(mg_word* p, uint32_t tag, uint32_t payload) {
-    const mg_word v = ((mg_word)tag << 32) | payload;
-    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long mg_globaltimer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ int mg_ld_flag(const int* p) {
-    int v;
-    asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-template <typename T>
-__device__ __forceinline__ T mg_from_float(float v);
-template <>
-__device__ __forceinline__ float mg_from_float<float>(float v) { return v; }
-template <>
-__device__ __forceinline__ __nv_bfloat16 mg_from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
-
-template <typename T>
-struct mg_vec;
-template <>
-struct mg_vec<float> {
-    static constexpr int N = 4;
-    __device__ __forceinline__ static void unpack(const uint4& v, float (&w)[4]) {
-        w[0] = __uint_as_float(v.x), w[1] = __uint_as_float(v.y), w[2] = __uint_as_float(v.z), w[3] = __uint_as_float(v.w);
-    }
-};
-template <>
-struct mg_vec<__nv_bfloat16> {
-    static constexpr int N = 8;
-    __device__ __forceinline__ static void unpack(const uint4& v, float (&w)[8]) {
-        const unsigned int u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            w[2 * i] = __uint_as_float(u[i] << 16);
-            w[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
-        }
-    }
-};
-
-// ---------------------------------------------------------------------------
-// CTA layout: warps 0-7 (256 threads) are consumers; warp 8 is the producer (one
-// elected lane issues the bulk copies).  Consumers synchronise among themselves
-// on named barrier 1, so the producer never has to take part.
-// ---------------------------------------------------------------------------
-#define MG_TOTAL_THREADS (MG_THREADS + 32)
-
-__device__ __forceinline__ void mg_csync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-__device__ __forceinline__ bool mg_csync_or(bool pred) {
-    uint32_t r;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-        : "=r"(r)
-        : "r"((uint32_t)(pred ? 1 : 0))
-        : "memory");
-    return r != 0;
-}
-__device__ __forceinline__ void mg_mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mg_smem(bar)) : "memory");
-}
-
-// Per-thread control state.  `dead` becomes CTA-wide at the next op boundary.
-struct mg_ctl {
-    int* abort_flag;
-    unsigned poll_sleep;  // ns to pause between two polls of words that were not valid yet (0 = none)
-    bool dead;
-};
-__device__ __forceinline__ void mg_give_up(mg_ctl& c) {
-    atomicExch(c.abort_flag, 1);
-    c.dead = true;
-}
-
-__device__ __forceinline__ int mg_attn_rows_per_chunk(int hd, int kvsize) { return MG_SLOT_BYTES / (hd * kvsize); }
-
-// Consumer view of the ring.
-struct mg_cons {
-    unsigned char* slots;
-    uint64_t *full, *empty;
-    int nslot, slot;
-    uint32_t parity;
-};
-__device__ __forceinline__ const unsigned char* mg_ring_wait(mg_cons& r, mg_ctl& ctl) {
-    uint32_t spins = 0;
-    while (!ctl.dead && !mg_mbar_try_wait(&r.full[r.slot], r.parity)) {
-        if (++spins > (MG_SPIN_LIMIT >> 3) || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) mg_give_up(ctl);
-    }
-    return r.slots + (size_t)r.slot * MG_SLOT_BYTES;
-}
-// Each consumer warp reports that it is done with the slot; the 8th report frees it.
-__device__ __forceinline__ void mg_ring_release(mg_cons& r) {
-    __syncwarp();
-    if ((threadIdx.x & 31) == 0) mg_mbar_arrive(&r.empty[r.slot]);
-    if (++r.slot == r.nslot) r.slot = 0, r.parity ^= 1u;
-}
 
 // The producer: walks the CTA's copy schedule for every token of the run, waits for
 // a free slot, issues the copy.  K/V rows below the current position are final only
@@ -268,7 +140,7 @@ __device__ void mg_producer(const mg_params& p, const mg_cdesc* cd, int ncd, con
                     const int need = tok * nops;
                     uint32_t spins = 0;
                     while (*s_progress < need) {
-                        if (++spins > MG_SPIN_LIMIT || *s_dead) {
+                        if (++spins > p.spin_limit || *s_dead) {
                             stop = true;
                             break;
                         }
@@ -288,7 +160,7 @@ __device__ void mg_producer(const mg_params& p, const mg_cdesc* cd, int ncd, con
             for (int j = 0; j < nch; j++) {
                 uint32_t spins = 0;
                 while (!mg_mbar_try_wait(&empty[slot], parity ^ 1u)) {
-                    if (++spins > (MG_SPIN_LIMIT >> 3) || *s_dead) {
+                    if (++spins > p.spin_limit || *s_dead) {
                         stop = true;
                         break;
                     }
@@ -316,144 +188,12 @@ __device__ void mg_producer(const mg_params& p, const mg_cdesc* cd, int ncd, con
         for (uint32_t i = 0; i < n; i++) {
             if (--slot < 0) slot = nslot - 1, parity ^= 1u;
             uint32_t spins = 0;
-            while (!mg_mbar_try_wait(&full[slot], parity) && ++spins < (MG_SPIN_LIMIT >> 3)) {
+            while (!mg_mbar_try_wait(&full[slot], parity) && ++spins < p.spin_limit) {
             }
         }
     }
 }
 
-__device__ __forceinline__ void mg_ld_word2(const mg_word* p, mg_word& a, mg_word& b) {
-    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
-}
-
-// Fetch one stage input vector of n values (n even) into dst (shared memory) from
-// tagged words (16-byte aligned), polling until every word carries `tag`.  A thread owns
-// the word pairs tid, tid + 256, ...; one 16-byte load brings a pair (each 8-byte half
-// carries its own tag, so the halves validate independently), up to U loads are issued
-// back to back before any is checked, and only the pairs that were not valid yet are
-// read again, after a short pause that keeps the polling traffic of 148 CTAs off the L2.
-template <int U = 8>
-__device__ __noinline__ void mg_fetch(const mg_word* src, int n, uint32_t tag, float* dst, mg_ctl& ctl) {
-    const int npair = n >> 1;
-    for (int base = threadIdx.x; base < npair; base += MG_THREADS * U) {
-        uint32_t pending = 0;
-#pragma unroll
-        for (int u = 0; u < U; u++)
-            if (base + u * MG_THREADS < npair) pending |= 1u << u;
-        uint32_t spins = 0;
-        while (pending != 0) {
-            mg_word w[U][2];
-#pragma unroll
-            for (int u = 0; u < U; u++)
-                if (pending & (1u << u)) mg_ld_word2(src + 2 * (base + u * MG_THREADS), w[u][0], w[u][1]);
-            uint32_t done = 0;
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                if ((pending & (1u << u)) && (uint32_t)(w[u][0] >> 32) == tag && (uint32_t)(w[u][1] >> 32) == tag) {
-                    const int i = 2 * (base + u * MG_THREADS);
-                    *reinterpret_cast<float2*>(dst + i) =
-                        make_float2(__uint_as_float((uint32_t)w[u][0]), __uint_as_float((uint32_t)w[u][1]));
-                    done |= 1u << u;
-                }
-            }
-            pending &= ~done;
-            if (pending != 0) {
-                if (++spins > MG_SPIN_LIMIT || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
-                    mg_give_up(ctl);
-                    break;
-                }
-                if (ctl.poll_sleep) __nanosleep(ctl.poll_sleep);
-            }
-        }
-        if (ctl.dead) break;
-    }
-}
-
-// Fetch of a stage input where every thread takes exactly the elements it will use itself: element k
-// belongs to thread k mod 256, the same thread that owns weight row k in the dot products.  Nothing else
-// reads dst[k], so no barrier is needed between this fetch and the dot products, and a thread starts its
-// multiply-adds as soon as ITS words have arrived.  8-byte loads, up to U in flight per thread.
-template <int U = 8>
-__device__ __noinline__ void mg_fetch_own(const mg_word* src, int n, uint32_t tag, float* dst, mg_ctl& ctl) {
-    for (int base = threadIdx.x; base < n; base += MG_THREADS * U) {
-        uint32_t pending = 0;
-#pragma unroll
-        for (int u = 0; u < U; u++)
-            if (base + u * MG_THREADS < n) pending |= 1u << u;
-        uint32_t spins = 0;
-        while (pending != 0) {
-            mg_word w[U];
-#pragma unroll
-            for (int u = 0; u < U; u++)
-                if (pending & (1u << u)) w[u] = mg_ld_word(src + base + u * MG_THREADS);
-            uint32_t done = 0;
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                if ((pending & (1u << u)) && (uint32_t)(w[u] >> 32) == tag) {
-                    dst[base + u * MG_THREADS] = __uint_as_float((uint32_t)w[u]);
-                    done |= 1u << u;
-                }
-            }
-            pending &= ~done;
-            if (pending != 0) {
-                if (++spins > MG_SPIN_LIMIT || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
-                    mg_give_up(ctl);
-                    break;
-                }
-                if (ctl.poll_sleep) __nanosleep(ctl.poll_sleep);
-            }
-        }
-        if (ctl.dead) break;
-    }
-}
-
-__device__ __forceinline__ float mg_block_max(float v, float* scratch) {
-    v = rg_warp_max(v);
-    mg_csync();
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    mg_csync();
-    float r = scratch[0];
-#pragma unroll
-    for (int i = 1; i < MG_THREADS / 32; i++) r = fmaxf(r, scratch[i]);
-    return r;
-}
-
-// Sum N per-lane values across the warp with a halving exchange: while N is even each
-// step sends half of the values to the partner lane and keeps the other half, so N
-// halves per step; the remaining steps are plain butterflies.  On return v[0..count)
-// of lane l holds the warp sums of indices base + [0, count).
-template <int N, int O>
-struct mg_halver {
-    __device__ __forceinline__ static void run(float (&v)[N], int lane, int& base, int& count) {
-        if constexpr (O == 0) {
-            count = N;
-        } else if constexpr (N % 2 == 0) {
-            constexpr int H = N / 2;
-            const bool upper = (lane & O) != 0;
-            float keep[H];
-#pragma unroll
-            for (int i = 0; i < H; i++) {
-                const float send = upper ? v[i] : v[i + H];
-                const float recv = __shfl_xor_sync(RG_FULL_MASK, send, O);
-                keep[i] = (upper ? v[i + H] : v[i]) + recv;
-            }
-            if (upper) base += H;
-            mg_halver<H, O / 2>::run(reinterpret_cast<float(&)[H]>(keep), lane, base, count);
-#pragma unroll
-            for (int i = 0; i < H; i++) v[i] = keep[i];
-        } else {
-#pragma unroll
-            for (int i = 0; i < N; i++) v[i] += __shfl_xor_sync(RG_FULL_MASK, v[i], O);
-            mg_halver<N, O / 2>::run(v, lane, base, count);
-        }
-    }
-    // lanes that differ only in bits consumed by plain butterflies hold identical sums: the lowest one writes
-    __device__ __forceinline__ static bool writer(int lane) {
-        int n = N, o = 16;
-        while (o > 0 && n % 2 == 0) n /= 2, o >>= 1;
-        return o == 0 || (lane & (2 * o - 1)) == 0;
-    }
-};
 
 // Dot products of one group (NQA active 16-byte column groups, all K rows) for B input
 // vectors: streams the group's chunks out of the ring, then sums the per-thread partials
@@ -467,6 +207,7 @@ __device__ __forceinline__ void mg_group_dots(const mg_op& op, mg_cons& ring, mg
                                               unsigned long long* tr_loop) {
     constexpr int UV = UB / (int)sizeof(WT);  // columns per unit
     constexpr int NV = B * NQA * UV;
+    __builtin_assume(__isShared(xs)), __builtin_assume(__isShared(red));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float acc[NV];
 #pragma unroll
@@ -577,6 +318,13 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
     float* awts = reinterpret_cast<float*>(sp);  // [256] normalised weights of the attention records
     sp += 256 * 4;
     float* pickbuf = reinterpret_cast<float*>(sp);  // [n_pick_ctas * B * 2]
+    // every one of these is a shared-memory pointer: say so, so that ld.shared / st.shared are emitted (see mg_ring_wait)
+    __builtin_assume(__isShared(slots)), __builtin_assume(__isShared(ops)), __builtin_assume(__isShared(cds));
+    __builtin_assume(__isShared(xs)), __builtin_assume(__isShared(xemb)), __builtin_assume(__isShared(go));
+    __builtin_assume(__isShared(xres)), __builtin_assume(__isShared(gml)), __builtin_assume(__isShared(sqkv));
+    __builtin_assume(__isShared(red2)), __builtin_assume(__isShared(scratch2)), __builtin_assume(__isShared(bestv));
+    __builtin_assume(__isShared(besti)), __builtin_assume(__isShared(s_pick)), __builtin_assume(__isShared(s_flags));
+    __builtin_assume(__isShared(awts)), __builtin_assume(__isShared(pickbuf));
 
     const int op0 = p.cta_off[cta];
     const int nops = p.cta_off[cta + 1] - op0;
@@ -607,6 +355,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
     mg_ctl ctl;
     ctl.abort_flag = p.abort_flag;
     ctl.poll_sleep = (unsigned)p.poll_sleep;
+    ctl.limit = p.spin_limit;
     ctl.dead = false;
     mg_cons ring;
     ring.slots = slots, ring.full = full, ring.empty = empty, ring.nslot = p.nslot, ring.slot = 0, ring.parity = 0;
@@ -681,6 +430,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
             // fetch and its dot products, a warp could otherwise overwrite partials the previous op's epilogue still reads.
             float* red = red2 + (oi & 1) * (NWARP * NOUT);
             float* scratch = scratch2 + (oi & 1) * (NWARP * 4 * MG_BMAX);
+            __builtin_assume(__isShared(red)), __builtin_assume(__isShared(scratch));
             const uint32_t tag = tagbase + (uint32_t)op.layer + 1u;
             const bool tracing = TRACE && p.trace != nullptr && t == p.n_steps - 1 && tid == 0;
             unsigned long long* tr = tracing ? p.trace + ((size_t)cta * p.max_ops + oi) * 8 : nullptr;
@@ -708,7 +458,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                     uint32_t spins = 0;
                     mg_word w = mg_ld_word(src);
                     while ((uint32_t)(w >> 32) != tag) {
-                        if (++spins > MG_SPIN_LIMIT || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
+                        if (++spins > ctl.limit || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
                             mg_give_up(ctl);
                             break;
                         }
@@ -939,6 +689,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
             const float* xin = xs;
             int xstride = XLEN;
             if (op.type == MG_OPROJ) xin = xs + ((B * p.H * p.S * (p.hd + 2) + 3) & ~3), xstride = p.D;
+            __builtin_assume(__isShared(xin));
             if (op.uv == VEC) {
                 switch (op.nq) {
                     case 1: mg_group_dots<WT, B, 1, 16, TRACE>(op, ring, ctl, xin, xstride, red, t0, t1, wait_cyc, tracing ? tr + 7 : nullptr); break;
@@ -992,7 +743,8 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                 s = ln_stage ? fmaf(rstd[b], fmaf(-mu[b], t1, s), t0) : s + t0;
                 const int col = op.q0 * op.uv + jq;
                 if (op.type == MG_QKV) {
-                    mg_st_word(p.buf_qkv + (size_t)b * 3 * p.D + col, tag, __float_as_uint(s));
+                    if (!(cta == 0 && op.layer == p.withhold_layer))
+                        mg_st_word(p.buf_qkv + (size_t)b * 3 * p.D + col, tag, __float_as_uint(s));
                 } else if (op.type == MG_OPROJ) {
                     const float v = xres[b * p.res_cap + op.aux + jq] + s;
                     xres[b * p.res_cap + op.aux + jq] = v;
@@ -1396,6 +1148,12 @@ rg_status rg_mega_create(rg_gpt* m) {
     return RG_OK;
 }
 
+void rg_mega_debug(rg_gpt* m, unsigned spin_limit, int withhold_layer) {
+    if (!m->mega) return;
+    if (spin_limit != 0xffffffffu) m->mega->spin_limit = spin_limit ? spin_limit : MG_SPIN_LIMIT;
+    if (withhold_layer != -3) m->mega->withhold_layer = withhold_layer;
+}
+
 void rg_mega_destroy(rg_gpt* m) {
     if (!m->mega) return;
     for (void* p : m->mega->allocs) cudaFree(p);
@@ -1427,6 +1185,7 @@ static rg_status mg_run_once(rg_gpt* m, int B, size_t pos0, size_t n_steps) {
     prm.act = m->cfg.activation;
     prm.pos0 = (int)pos0, prm.n_steps = (int)n_steps, prm.epoch0 = m->epoch;
     prm.S = g->S;
+    prm.spin_limit = g->spin_limit, prm.withhold_layer = g->withhold_layer;
     {
         const char* ps = getenv("RG_B200_POLL_SLEEP_NS");
         prm.poll_sleep = ps ? atoi(ps) : 0;

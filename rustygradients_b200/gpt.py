@@ -118,6 +118,7 @@ class GPTModel:
         B, T = ids.shape
         logits = np.empty((B, self.config.vocab_size), dtype=np.float32) if want_logits else None
         pick = np.empty(B, dtype=np.uint32)
+        self._batch = B                      # sequences of the cached context: decode_step / rewind take one id each
         check(self._lib.rg_gpt_prefill(self._h, ids.ctypes.data_as(_lib._U32P), B, T,
                                        logits.ctypes.data_as(_lib._FP) if want_logits else None,
                                        pick.ctypes.data_as(_lib._U32P)))
@@ -126,6 +127,9 @@ class GPTModel:
     def decode_step(self, tok: np.ndarray, want_logits: bool = True):
         tok = np.ascontiguousarray(tok, dtype=np.uint32).reshape(-1)
         B = tok.size
+        cached = getattr(self, "_batch", None)
+        if cached is not None and B != cached:   # the library reads one id per cached sequence from this array
+            raise _lib.InvalidInput(f"decode_step got {B} ids for a context of {cached} sequences")
         logits = np.empty((B, self.config.vocab_size), dtype=np.float32) if want_logits else None
         pick = np.empty(B, dtype=np.uint32)
         check(self._lib.rg_gpt_decode_step(self._h, tok.ctypes.data_as(_lib._U32P),
@@ -139,6 +143,9 @@ class GPTModel:
     def rewind(self, T: int, tok: Optional[np.ndarray] = None) -> None:
         if tok is not None:
             tok = np.ascontiguousarray(tok, dtype=np.uint32).reshape(-1)
+            cached = getattr(self, "_batch", None)
+            if cached is not None and tok.size != cached:
+                raise _lib.InvalidInput(f"rewind got {tok.size} ids for a context of {cached} sequences")
         check(self._lib.rg_gpt_rewind(self._h, int(T), tok.ctypes.data_as(_lib._U32P) if tok is not None else None))
 
     def read_tokens(self, start: int, n: int, batch: int) -> np.ndarray:
@@ -177,6 +184,10 @@ class GPTModel:
         n = C.c_size_t(0)
         check(self._lib.rg_gpt_trace_read(self._h, out.ctypes.data_as(C.POINTER(C.c_uint64)), cap_rows, C.byref(n)))
         return out[: n.value]
+
+    def debug_hook(self, what: int, value: int = 0) -> None:
+        """Test hook of the bounded device waits (rg_debug_hook; the header lists the values of `what`)."""
+        check(self._lib.rg_debug_hook(self.backend._ctx, self._h, int(what), int(value)))
 
     def decode_step_bytes(self, batch: int, mean_ctx: float) -> float:
         return float(self._lib.rg_gpt_decode_step_bytes(self._h, int(batch), float(mean_ctx)))

@@ -5,7 +5,10 @@ import rustygradients_b200 as rg
 from oracle import gpt_oracle as O
 
 F32_TOL = 1e-3      # max |logit difference| in f32 mode, every step
-BF16_REL_TOL = 2e-2  # relative to the largest |logit| of the row, bf16-weight mode
+BF16_REL_TOL = 2e-2  # the stated bound of bf16-weight mode ("rel <= 2e-2")
+# What the tests assert in bf16-weight mode: max |difference| of a logits row divided by the row's largest |logit|
+# (the reading of "rel" used throughout), at a bound close to what is measured (2e-3 ... 6e-3) rather than the stated 2e-2.
+BF16_ROW_TOL = 8e-3
 
 
 def model_for(backend, cfg: O.GptConfig, params, causal=True, act="gelu_tanh", dtype="f32", max_batch=1):
@@ -34,3 +37,22 @@ def confident_rows(logits: np.ndarray, margin: float):
     """Rows whose top-2 gap exceeds margin (argmax there must agree bit-exactly)."""
     s = np.sort(logits, axis=-1)
     return (s[..., -1] - s[..., -2]) > margin
+
+
+def bf16_row_errors(logits: np.ndarray, want: np.ndarray):
+    """(max-norm error, RMS error) of every logits row, both relative to the oracle's row."""
+    d = (logits - want).astype(np.float64)
+    w = want.astype(np.float64)
+    mx = np.abs(d).max(-1) / np.abs(w).max(-1)
+    rms = np.sqrt((d * d).mean(-1)) / np.sqrt((w * w).mean(-1))
+    return mx, rms
+
+
+def assert_bf16_close(logits: np.ndarray, want: np.ndarray, what: str = ""):
+    """bf16-weight mode against the oracle: every row within BF16_ROW_TOL (and therefore within the stated 2e-2);
+    prints the worst row's errors so that a run shows how far from the bound it is."""
+    mx, rms = bf16_row_errors(logits, want)
+    print(f"bf16 parity {what}: worst row max-norm rel {mx.max():.2e}, worst row RMS rel {rms.max():.2e} "
+          f"(bound {BF16_ROW_TOL:.0e}, stated {BF16_REL_TOL:.0e})")
+    assert mx.max() <= BF16_ROW_TOL, (what, float(mx.max()))
+    assert rms.max() <= BF16_REL_TOL, (what, float(rms.max()))

@@ -8,7 +8,7 @@ import pytest
 
 import rustygradients_b200 as rg
 from oracle import gpt_oracle as O
-from helpers import BF16_REL_TOL, F32_TOL, confident_rows, model_for, teacher_forced
+from helpers import BF16_REL_TOL, F32_TOL, assert_bf16_close, confident_rows, model_for, teacher_forced
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
@@ -122,20 +122,42 @@ def test_gpt2_small_reference_mode(backend):
 
 
 # ---- bf16-weight mode and batches (configurations 2-4 at reduced depth / batch)
-@pytest.mark.parametrize("shape", [(50257, 768, 12, 2), (50257, 1024, 16, 2), (5003, 1600, 25, 1)])
+@pytest.mark.parametrize("shape", [(50257, 768, 12, 2), (50257, 1024, 16, 2), (5003, 1600, 25, 2)])
 def test_bf16_batched_steps(backend, shape):
+    """bf16 weights, GPT-2 small / medium / XL widths at reduced depth, against the ORACLE for every form of the token
+    step: batches 1, 2, 4 run in the persistent kernel, batch 5 as separate launches."""
     V, D, H, L = shape
     cfg = O.GptConfig(64, V, L, H, D)
-    B, P, G = 5, 24, 6
+    P, G = 24, 6
     params = O.make_params(cfg, 77, stress=True, bf16=True)
-    prompt = O.make_prompt(cfg, 77, B, P)
-    toks, want = O.generate_causal(params, cfg, prompt, G)
     m = model_for(backend, cfg, params, dtype="bf16", max_batch=8)
-    ids = np.concatenate([prompt, toks], 1)
-    logits, picks = teacher_forced(m, ids, P)
-    scale = np.abs(want).max(-1, keepdims=True)
-    assert (np.abs(logits - want) / scale).max() <= BF16_REL_TOL
-    assert np.array_equal(picks, logits.argmax(-1))
+    for B in (1, 2, 4, 5):
+        prompt = O.make_prompt(cfg, 77 + B, B, P)
+        toks, want = O.generate_causal(params, cfg, prompt, G)
+        ids = np.concatenate([prompt, toks], 1)
+        logits, picks = teacher_forced(m, ids, P)
+        assert_bf16_close(logits, want, f"D={D} H={H} batch {B}")
+        assert np.array_equal(picks, logits.argmax(-1))
+
+
+@pytest.mark.parametrize("shape", [(1024, 16), (1600, 25)])
+def test_f32_persistent_kernel_wide_models(backend, shape):
+    """The persistent kernel (batches 1, 2, 4) on the medium and XL widths, f32, 2 layers, against the oracle."""
+    D, H = shape
+    cfg = O.GptConfig(48, 3001, 2, H, D)
+    params = O.make_params(cfg, 31, stress=True)
+    m = model_for(backend, cfg, params, max_batch=4)
+    for B in (1, 2, 4):
+        prompt = O.make_prompt(cfg, 31 + B, B, 11)
+        toks, want = O.generate_causal(params, cfg, prompt, 8)
+        logits, picks = teacher_forced(m, np.concatenate([prompt, toks], 1), 11)
+        assert np.abs(logits - want).max() <= F32_TOL, (D, B, float(np.abs(logits - want).max()))
+        assert np.array_equal(picks, logits.argmax(-1))
+        l0 = backend.launch_count
+        m.rewind(11)
+        m.decode_run(6)
+        backend.synchronize()
+        assert backend.launch_count - l0 <= 3          # the persistent kernel took it: one launch for 6 steps
 
 
 def test_f32_batched_steps_odd_sizes(backend):
@@ -167,15 +189,14 @@ def test_full_size_cache_is_consistent_with_recompute(backend):
     m.prefill(ids[:, :P])
     for t in range(P, P + G - 1):
         lg_step, pk_step = m.decode_step(ids[:, t])
-    scale = np.abs(lg_pre).max(-1, keepdims=True)
-    assert (np.abs(lg_step - lg_pre) / scale).max() <= BF16_REL_TOL
+    assert_bf16_close(lg_step, lg_pre, "batch 64: cached step vs prompt pass")
     # shards of the batch are independent: sequence b alone gives the same ids
     solo = m.generate(prompt[7:9], G)
     assert np.array_equal(solo, out[7:9])
     # the oracle on two of the 64 sequences, first step
     want = O.forward(params, cfg, prompt[:2], causal=True, act="gelu_tanh", last_only=True)[:, 0]
     lg0, _ = m.prefill(prompt[:2])
-    assert (np.abs(lg0 - want) / np.abs(want).max(-1, keepdims=True)).max() <= BF16_REL_TOL
+    assert_bf16_close(lg0, want, "full-size prompt pass")
 
 
 # ---- error behaviour of the model interface
@@ -202,6 +223,9 @@ def test_model_errors(backend):
         m.prefill(np.zeros((3, 4), np.uint32))  # batch > max_batch
     with pytest.raises(rg.InvalidInput):
         m.decode_step(np.array([1]))            # no context yet
+    m.prefill(np.zeros((1, 15), np.uint32))
+    with pytest.raises(rg.InvalidInput):
+        m.decode_step(np.array([1, 2]))         # two ids for a context of one sequence
     m.prefill(np.zeros((1, 16), np.uint32))
     with pytest.raises(rg.ContextFull):
         m.decode_step(np.array([1]))
@@ -329,7 +353,7 @@ def test_fused_rows_step_equals_plain_rows_step(backend, monkeypatch):
         assert (np.abs(la - lb) / scale).max() <= 8e-3
         assert np.array_equal(pa, la.argmax(-1)) and np.array_equal(pb, lb.argmax(-1))
         want = O.teacher_forced_logits(params, cfg, ids, True, "gelu_tanh", 9)
-        assert (np.abs(la - want) / np.abs(want).max(-1, keepdims=True)).max() <= BF16_REL_TOL
+        assert_bf16_close(la, want, f"fused rows step batch {B}")
 
 
 # ---- prompt pass in bf16 mode: tensor-core projections and attention against the CUDA-core kernels and the oracle
@@ -350,9 +374,8 @@ def test_prompt_pass_tensor_core_kernels(backend, monkeypatch, causal):
         lb = b.forward(ids.astype(np.float32))
         monkeypatch.delenv("RG_B200_PREFILL", raising=False)
         want = O.forward(params, cfg, ids, causal=causal, act=act)
-        scale = np.abs(want).max(-1, keepdims=True)
-        assert (np.abs(lb - want) / scale).max() <= BF16_REL_TOL
-        assert (np.abs(la - want) / scale).max() <= BF16_REL_TOL
+        assert_bf16_close(lb, want, f"prompt pass CUDA cores B={B} T={T}")
+        assert_bf16_close(la, want, f"prompt pass tensor cores B={B} T={T}")
         assert np.isfinite(la).all()
         # launch counts tell that the tensor-core attention ran: one more kernel per block (the Q / V^T preparation)
         l0 = backend.launch_count

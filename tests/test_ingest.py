@@ -195,6 +195,14 @@ def test_ingest_errors(backend, tmp_path):
         f.write(struct.pack("<Q", 1 << 40) + b"{}")
     with pytest.raises(rg.SerializationError):
         m.load_safetensors(path)
+    # a shape whose element count wraps around 64 bits (4 * 2^62 bytes = 0), with and without an aligned header
+    for pad in (0, 1):
+        hdr = json.dumps({"token_embedding.weight": {"dtype": "F32", "shape": [1 << 62], "data_offsets": [0, 0]}}).encode()
+        hdr += b" " * ((-len(hdr) % 8) + pad)
+        with open(path, "wb") as f:
+            f.write(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 16)
+        with pytest.raises(rg.SerializationError):
+            m.load_safetensors(path)
     # JSON: wrong tensor count, wrong shape, data length that does not match the shape
     jpath = str(tmp_path / "w.json")
     S.write_weights_json(jpath, params[:-1])

@@ -50,6 +50,17 @@ def test_noalloc_projection_matches_matmul_twice(backend):
         assert np.isfinite(got).all()
         assert np.abs(got - want).max() <= 1e-3          # the f32 tolerance of the parity tests
         assert np.abs(got - (x.astype(np.float64) @ w + b)).max() <= 1e-3
+    # odd sizes and no bias: K neither a multiple of 8 nor of the k-split, N not a multiple of the column tile
+    K, N = 773, 132
+    x = rng.standard_normal(K).astype(np.float32)
+    w = (rng.standard_normal((K, N)) * 0.05).astype(np.float32)
+    tx, tw = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
+    ty = torch.full((N,), float("nan"), device=dev)
+    torch.cuda.synchronize(dev)
+    _lib.check(lib.rg_linear_row_noalloc(C.c_void_p(tx.data_ptr()), C.c_void_p(tw.data_ptr()), None, C.c_void_p(ty.data_ptr()),
+                                         K, N, C.c_void_p(stream.cuda_stream)))
+    torch.cuda.synchronize(dev)
+    assert np.abs(ty.cpu().numpy() - x.astype(np.float64) @ w).max() <= 1e-3
     # sizes beyond the built-in scratch are refused with a clear message, not truncated
     st = lib.rg_linear_row_noalloc(C.c_void_p(tx.data_ptr()), C.c_void_p(tw.data_ptr()), None, C.c_void_p(ty.data_ptr()),
                                    16, 16388, C.c_void_p(stream.cuda_stream))
