@@ -158,7 +158,9 @@ __device__ __forceinline__ void mg_ld_word2(const mg_word* p, mg_word& a, mg_wor
 // carries its own tag, so the halves validate independently), up to U loads are issued
 // back to back before any is checked, and only the pairs that were not valid yet are
 // read again, after a short pause that keeps the polling traffic of 148 CTAs off the L2.
-template <int U = 8>
+// RT = false compiles the wait limit in and leaves the optional pause out (the noinline routines would otherwise read
+// both from the caller's stack inside the polling loop: 3 % of the token time on the GPT-2-small shape).
+template <int U = 8, bool RT = true>
 __device__ __noinline__ void mg_fetch(const mg_word* src, int n, uint32_t tag, float* dst, mg_ctl& ctl) {
     __builtin_assume(__isShared(dst));
     const int npair = n >> 1;
@@ -185,11 +187,11 @@ __device__ __noinline__ void mg_fetch(const mg_word* src, int n, uint32_t tag, f
             }
             pending &= ~done;
             if (pending != 0) {
-                if (++spins > ctl.limit || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
+                if (++spins > (RT ? ctl.limit : MG_SPIN_LIMIT) || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
                     mg_give_up(ctl);
                     break;
                 }
-                if (ctl.poll_sleep) __nanosleep(ctl.poll_sleep);
+                if (RT && ctl.poll_sleep) __nanosleep(ctl.poll_sleep);
             }
         }
         if (ctl.dead) break;
@@ -200,7 +202,7 @@ __device__ __noinline__ void mg_fetch(const mg_word* src, int n, uint32_t tag, f
 // belongs to thread k mod 256, the same thread that owns weight row k in the dot products.  Nothing else
 // reads dst[k], so no barrier is needed between this fetch and the dot products, and a thread starts its
 // multiply-adds as soon as ITS words have arrived.  8-byte loads, up to U in flight per thread.
-template <int U = 8>
+template <int U = 8, bool RT = true>
 __device__ __noinline__ void mg_fetch_own(const mg_word* src, int n, uint32_t tag, float* dst, mg_ctl& ctl) {
     __builtin_assume(__isShared(dst));
     for (int base = threadIdx.x; base < n; base += MG_THREADS * U) {
@@ -224,11 +226,11 @@ __device__ __noinline__ void mg_fetch_own(const mg_word* src, int n, uint32_t ta
             }
             pending &= ~done;
             if (pending != 0) {
-                if (++spins > ctl.limit || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
+                if (++spins > (RT ? ctl.limit : MG_SPIN_LIMIT) || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
                     mg_give_up(ctl);
                     break;
                 }
-                if (ctl.poll_sleep) __nanosleep(ctl.poll_sleep);
+                if (RT && ctl.poll_sleep) __nanosleep(ctl.poll_sleep);
             }
         }
         if (ctl.dead) break;

@@ -354,8 +354,8 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
     // =================== consumer warps ===================
     mg_ctl ctl;
     ctl.abort_flag = p.abort_flag;
-    ctl.poll_sleep = (unsigned)p.poll_sleep;
-    ctl.limit = p.spin_limit;
+    ctl.poll_sleep = TRACE ? (unsigned)p.poll_sleep : 0u;
+    ctl.limit = TRACE ? p.spin_limit : MG_SPIN_LIMIT;  // a run-time limit costs 3 % of the token time: instrumented build only
     ctl.dead = false;
     mg_cons ring;
     ring.slots = slots, ring.full = full, ring.empty = empty, ring.nslot = p.nslot, ring.slot = 0, ring.parity = 0;
@@ -609,7 +609,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                         if (local) {
                             for (int i = tid; i < n_in; i += MG_THREADS) xr[i] = xemb[b * p.D + i];
                         } else {
-                            mg_fetch_own<4>(src + (size_t)b * n_in, n_in, in_tag, xr, ctl);
+                            mg_fetch_own<4, TRACE>(src + (size_t)b * n_in, n_in, in_tag, xr, ctl);
                         }
                         const float c = __shfl_sync(RG_FULL_MASK, tid < n_in ? xr[tid] : 0.f, 0);  // lane 0 of a warp always owns an element when n >= 256
                         float s0 = 0.f, s1 = 0.f, s2 = 0.f;
@@ -631,7 +631,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                 } else if (op.type == MG_OPROJ) {
                     // attention records of every (sequence, head, slice) -> merged, normalised head outputs
                     const int rec = p.hd + 2, nrec = B * p.H * p.S * rec;
-                    mg_fetch<8>(p.buf_a, nrec, in_tag, xs, ctl);
+                    mg_fetch<8, TRACE>(p.buf_a, nrec, in_tag, xs, ctl);
                     mg_csync();
                     if (tracing) tr[6] = mg_globaltimer();
                     float* vec = xs + ((nrec + 3) & ~3);
@@ -678,7 +678,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                     }
                 } else {
 #pragma unroll
-                    for (int b = 0; b < B; b++) mg_fetch_own<16>(src + (size_t)b * n_in, n_in, in_tag, xs + b * XLEN, ctl);
+                    for (int b = 0; b < B; b++) mg_fetch_own<16, TRACE>(src + (size_t)b * n_in, n_in, in_tag, xs + b * XLEN, ctl);
                     if (tracing) tr[6] = mg_globaltimer();
                 }
                 if constexpr (TRACE) poll_cyc += clock64() - c0;
@@ -743,7 +743,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                 s = ln_stage ? fmaf(rstd[b], fmaf(-mu[b], t1, s), t0) : s + t0;
                 const int col = op.q0 * op.uv + jq;
                 if (op.type == MG_QKV) {
-                    if (!(cta == 0 && op.layer == p.withhold_layer))
+                    if (!(TRACE && cta == 0 && op.layer == p.withhold_layer))
                         mg_st_word(p.buf_qkv + (size_t)b * 3 * p.D + col, tag, __float_as_uint(s));
                 } else if (op.type == MG_OPROJ) {
                     const float v = xres[b * p.res_cap + op.aux + jq] + s;
@@ -785,7 +785,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
         flush_append();
 
         // ---- greedy pick (top_k = 1 of src/wasm_api.rs:120-156): best over all CTAs, lowest index on ties ----
-        mg_fetch<8>(p.buf_pick, p.n_pick_ctas * B * 2, tagbase + (uint32_t)p.L + 1u, pickbuf, ctl);
+        mg_fetch<8, TRACE>(p.buf_pick, p.n_pick_ctas * B * 2, tagbase + (uint32_t)p.L + 1u, pickbuf, ctl);
         // everything any CTA stored before its pick (cache rows included) is ordered before what follows here
         __threadfence();
         mg_fence_proxy_async();
@@ -1048,7 +1048,9 @@ static cudaError_t mg_launch_t(rg_gpt* m, rg_mega* g, mg_params& prm) {
 
 template <typename WT, int B, int NQ>
 static cudaError_t mg_launch(rg_gpt* m, rg_mega* g, mg_params& prm) {
-    return prm.trace ? mg_launch_t<WT, B, NQ, true>(m, g, prm) : mg_launch_t<WT, B, NQ, false>(m, g, prm);
+    // the instrumented build is also the one that honours a lowered wait limit and the withheld signal of the tests
+    const bool instrumented = prm.trace || prm.spin_limit != MG_SPIN_LIMIT || prm.withhold_layer != -1 || prm.poll_sleep;
+    return instrumented ? mg_launch_t<WT, B, NQ, true>(m, g, prm) : mg_launch_t<WT, B, NQ, false>(m, g, prm);
 }
 
 // Where the exchange buffers sit inside their allocation decides which L2 slices serve the words that all 148 CTAs
