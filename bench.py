@@ -391,7 +391,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                        "parallelism": f"{world} independent sequence shard(s), no collective in the loop"},
             "us_per_token": t_step * 1e6,
             "roofline": {"bound": "hbm",
-                         "kernel": ("rg_token_loop_kernel: one persistent cooperative launch per step (256 token-loop iterations)"
+                         "kernel": ((("rg_cluster_loop_kernel" if os.environ.get("RG_B200_DECODE") == "cluster" else "rg_token_loop_kernel")
+                                     + f": one persistent cooperative launch per step ({G} token-loop iterations)")
                                     if launches <= 2 * args.steps else
                                     f"token step = {launches // (args.steps * G)} kernels replayed as one CUDA graph"),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
