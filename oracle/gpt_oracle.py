@@ -321,6 +321,33 @@ def sample_topk(logits: np.ndarray, temperature: float, top_k: int, u: float) ->
     return 0
 
 
+def weighted_index_sample(weights: np.ndarray, u: float) -> int:
+    """`WeightedIndex::new(&probs).sample(rng)` as src/bin/knowledge_manager.rs:196-198 uses it.  The algorithm
+    lives in the `rand` crate (Cargo.toml pins rand 0.8.5; not vendored in the reference tree), restated from its
+    published description: `new` keeps the running f32 sums of all weights but the last and the total; `sample` draws
+    `chosen` uniformly in [0, total) and returns the number of kept sums that are <= chosen (a binary search).  `u` in
+    [0,1) stands for the reference's unseeded `thread_rng` draw (chosen = u * total).  The weights are
+    `exp(logit / temperature)` without normalisation or max subtraction."""
+    w = np.asarray(weights, F32)
+    c = F32(0)
+    cum = np.empty(w.shape[0], F32)
+    for i, v in enumerate(w):
+        c = F32(c + v)
+        cum[i] = c
+    total = cum[-1]
+    if not (total > 0) or not np.isfinite(total):
+        raise ValueError("WeightedIndex::new fails on an all-zero, negative or non-finite weight vector")
+    chosen = F32(F32(u) * total)
+    return int(np.searchsorted(cum[:-1], chosen, side="right"))
+
+
+def sample_weighted(logits: np.ndarray, temperature: float, u: float) -> int:
+    """One step of KnowledgeManager::generate's draw (src/bin/knowledge_manager.rs:196-198) from a row of logits."""
+    with np.errstate(over="ignore"):
+        w = np.exp((logits.astype(F32) / F32(temperature)).astype(F32)).astype(F32)
+    return weighted_index_sample(w, u)
+
+
 _M64 = (1 << 64) - 1
 
 

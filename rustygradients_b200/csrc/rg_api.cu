@@ -30,7 +30,12 @@ rg_devbuf::~rg_devbuf() {
         int cur = 0;
         cudaGetDevice(&cur);
         if (cur != device) cudaSetDevice(device);
-        cudaFree(ptr);
+        // the context's stream still exists: stream-ordered free; else (context destroyed first, which synchronised
+        // the stream) a plain free
+        if (!(ctx_alive && *ctx_alive && cudaFreeAsync(ptr, stream) == cudaSuccess)) {
+            cudaGetLastError();
+            cudaFree(ptr);
+        }
         if (cur != device) cudaSetDevice(cur);
     }
 }
@@ -63,6 +68,14 @@ extern "C" rg_status rg_ctx_create(int device, rg_ctx** out) {
     c->device = device;
     c->sm_count = prop.multiProcessorCount;
     cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) {
+        // keep freed op outputs in the device's pool instead of returning them to the driver at every synchronise
+        cudaMemPool_t pool = nullptr;
+        unsigned long long keep = ~0ull;
+        if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess)
+            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+        cudaGetLastError();
+    }
     if (e == cudaSuccess) e = cudaMalloc(&c->d_flag, sizeof(int) * 4);
     if (e == cudaSuccess) e = cudaMemset(c->d_flag, 0, sizeof(int) * 4);
     if (e == cudaSuccess) e = cudaMallocHost(&c->h_flag, sizeof(int) * 4);
@@ -78,6 +91,7 @@ extern "C" rg_status rg_ctx_destroy(rg_ctx* ctx) {
     if (!ctx) return RG_OK;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    *ctx->alive = false;
     cudaStreamDestroy(ctx->stream);
     cudaFree(ctx->d_flag);
     cudaFree(ctx->tc_ws);
@@ -126,8 +140,11 @@ rg_status rg_alloc_storage(rg_ctx* ctx, const size_t* shape, int ndim, rg_storag
     s->buf = std::make_shared<rg_devbuf>();
     s->buf->device = ctx->device;
     s->buf->bytes = (s->len ? s->len : 1) * sizeof(float);
-    cudaError_t e = cudaMalloc(&s->buf->ptr, s->buf->bytes);
+    s->buf->stream = ctx->stream;
+    s->buf->ctx_alive = ctx->alive;
+    cudaError_t e = cudaMallocAsync(&s->buf->ptr, s->buf->bytes, ctx->stream);
     if (e != cudaSuccess) {
+        cudaGetLastError();
         const size_t want = s->buf->bytes;
         s->buf->ptr = nullptr;
         delete s;

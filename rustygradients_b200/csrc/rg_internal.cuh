@@ -51,12 +51,19 @@ struct rg_ctx {
     bool pdl = false;        // launch with programmatic stream serialization (inside a chain of rg_pdl_sync kernels)
     float* tc_ws = nullptr;  // split-k workspace of the tensor-core GEMM (this context's stream only)
     size_t tc_ws_bytes = 0;
+    // storages outlive nothing they need: a buffer frees itself on `stream` only while this is still true
+    std::shared_ptr<bool> alive = std::make_shared<bool>(true);
 };
 
+// Op outputs come from the device's stream-ordered pool (cudaMallocAsync on the context's stream: a few microseconds
+// against the ~0.5 ms of a cudaMalloc / cudaFree pair, which dominated every small op) and go back to it on the same
+// stream, after the work that was enqueued on them.
 struct rg_devbuf {
     void* ptr = nullptr;
     size_t bytes = 0;
     int device = 0;
+    cudaStream_t stream = nullptr;
+    std::shared_ptr<bool> ctx_alive;
     ~rg_devbuf();
 };
 

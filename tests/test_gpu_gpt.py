@@ -249,7 +249,7 @@ def test_topk_temperature_sampling(backend):
         assert np.array_equal(out, m.generate(prompt, G, temperature=temperature, top_k=top_k, seed=seed))   # reproducible
         ids = np.concatenate([prompt, out], 1)
         logits, _ = teacher_forced(m, ids, P)            # the rows each draw was made from
-        agree = 0
+        agree = agree_wi = 0
         for b in range(B):
             for i in range(G):
                 lg = logits[b, i].astype(np.float64)
@@ -265,7 +265,10 @@ def test_topk_temperature_sampling(backend):
                 lo = cdf[tok - 1] if tok else 0.0
                 assert lo - 1e-5 <= u <= cdf[tok] + 1e-5          # the inverse-CDF walk stopped at the right id
                 agree += O.sample_topk(logits[b, i], temperature, top_k, u) == tok
+                if top_k == 0:      # KnowledgeManager::generate's WeightedIndex draw: same CDF, same id away from boundaries
+                    agree_wi += O.sample_weighted(logits[b, i], temperature, u) == tok
         assert agree >= B * G - 2                                   # the oracle's f32 walk agrees away from boundaries
+        assert top_k != 0 or agree_wi >= B * G - 2
     assert not np.array_equal(m.generate(prompt, G, temperature=1.0, top_k=50, seed=1),
                               m.generate(prompt, G, temperature=1.0, top_k=50, seed=2))
     assert np.array_equal(m.generate(prompt, G, temperature=5.0, top_k=1, seed=7), m.generate(prompt, G))  # top_k 1 is greedy

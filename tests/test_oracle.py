@@ -200,3 +200,33 @@ def test_bf16_round():
     r = O.bf16_round(x)
     t = torch.from_numpy(x).bfloat16().float().numpy()
     assert np.array_equal(r, t)
+
+
+def test_weighted_index_draw_is_the_top_k_0_draw():
+    """KnowledgeManager::generate (WeightedIndex over exp(l / T)) and WasmGptTrainer::generate with top_k = 0 (normalised
+    inverse-CDF walk) draw from the same distribution: for the same uniform number they return the same id unless the
+    number falls within f32 rounding of a CDF step, and then the neighbouring id."""
+    rng = np.random.default_rng(7)
+    V = 97
+    same = total = 0
+    for trial in range(40):
+        logits = (rng.standard_normal(V) * 1.5).astype(np.float32)
+        T = (0.7, 1.0, 1.3)[trial % 3]
+        for u in rng.random(25):
+            a = O.sample_weighted(logits, T, float(u))
+            b = O.sample_topk(logits, T, 0, float(u))
+            total += 1
+            same += a == b
+            assert abs(a - b) <= 1
+    assert same >= total - 2
+    # the edges of the binary search: u = 0 gives the first id with a positive weight, u just below 1 the last id
+    w = np.array([0.0, 2.0, 0.0, 1.0, 1.0], np.float32)
+    assert O.weighted_index_sample(w, 0.0) == 1
+    assert O.weighted_index_sample(w, 0.49) == 1 and O.weighted_index_sample(w, 0.5) == 3
+    assert O.weighted_index_sample(w, 0.75) == 4 and O.weighted_index_sample(w, 0.999999) == 4
+    # frequencies follow the weights
+    draws = np.array([O.weighted_index_sample(w, float(u)) for u in rng.random(4000)])
+    freq = np.bincount(draws, minlength=5) / 4000
+    assert np.abs(freq - w / w.sum()).max() < 0.03
+    with pytest.raises(ValueError):
+        O.weighted_index_sample(np.zeros(4, np.float32), 0.3)
