@@ -75,7 +75,11 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
 rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const tc_epi e) {
-    rg_pdl_sync();
+    // Inside a chain of dependent launches this kernel may start while its predecessor still runs.  Everything that does
+    // not depend on the predecessor happens before the wait: barrier set-up, the TMEM allocation and the copies of the
+    // WEIGHT tiles of the first TC_STAGES k-blocks (weights are never written by a kernel of the chain).  The activation
+    // tiles, the residual reads and every store come after it.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ unsigned char tc_smem_raw[];
     // 1024-byte aligned tiles (the swizzle pattern is a function of the address)
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -111,6 +115,26 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
+    // weight tiles of the first k-blocks (the `empty` barriers of a fresh ring pass without a wait)
+    uint32_t pre = 0;
+    if (warp == 0 && lane == 0) {
+        for (int tile = blockIdx.x; tile < ntiles && pre < TC_STAGES; tile += gridDim.x) {
+            const int n0 = (tile % tiles_n) * TC_BN;
+            for (int kb = 0; kb < nkb && pre < TC_STAGES; kb++, pre++) {
+                unsigned char* b_dst = tiles + pre * TC_STAGE_BYTES + TC_BM * TC_BK * 2;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full[pre])),
+                             "r"((uint32_t)TC_STAGE_BYTES)
+                             : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                        tc_smem(b_dst)),
+                    "l"(&tmB), "r"((kb_begin + kb) * TC_BK), "r"(n0), "r"(tc_smem(&full[pre]))
+                    : "memory");
+            }
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
     // Persistent tile loop: CTA x takes tiles x, x + gridDim.x, ...; n varies fastest, so the CTAs running at the same
     // time share rows of A in L2.  The three roles walk the same sequence, each with its own counters.
     if (warp == 0) {
@@ -123,19 +147,21 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 for (int kb = 0; kb < nkb; kb++, it++) {
                     const int s = it % TC_STAGES;
                     const uint32_t par = (it / TC_STAGES) & 1;
-                    ok = tc_wait(&empty[s], par ^ 1u, e.err);
-                    if (!ok) break;
                     unsigned char* a_dst = tiles + s * TC_STAGE_BYTES;
                     unsigned char* b_dst = a_dst + TC_BM * TC_BK * 2;
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full[s])),
-                                 "r"((uint32_t)TC_STAGE_BYTES)
-                                 : "memory");
+                    if (it >= pre) {
+                        ok = tc_wait(&empty[s], par ^ 1u, e.err);
+                        if (!ok) break;
+                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full[s])),
+                                     "r"((uint32_t)TC_STAGE_BYTES)
+                                     : "memory");
+                    }
                     asm volatile(
                         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                             tc_smem(a_dst)),
                         "l"(&tmA), "r"((kb_begin + kb) * TC_BK), "r"(m0), "r"(tc_smem(&full[s]))
                         : "memory");
-                    asm volatile(
+                    if (it >= pre) asm volatile(
                         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                             tc_smem(b_dst)),
                         "l"(&tmB), "r"((kb_begin + kb) * TC_BK), "r"(n0), "r"(tc_smem(&full[s]))
