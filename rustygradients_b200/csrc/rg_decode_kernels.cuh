@@ -245,7 +245,25 @@ struct rg_attn_step_args {
 
 template <typename KT, int HD>
 __global__ void __launch_bounds__(128) rg_attn_step_kernel(rg_attn_step_args p) {
-    rg_pdl_sync();
+    // Inside a launch chain this kernel may start while the QKV projection before it still runs.  The cached rows it
+    // will stream do not depend on that projection, so the CTA asks for its slice of K and V to be brought into L2
+    // before it waits.  The position read here may be one step old (the counter is advanced by an earlier kernel of the
+    // chain): it only sizes the hint; everything that matters is read again after the wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x == 0) {
+        const int hint = min(max(*reinterpret_cast<const volatile int*>(p.pos), 0), p.C - 1) + 1;
+        const int hchunk = (hint + p.NS - 1) / p.NS;
+        const int h0 = (int)blockIdx.x * hchunk, h1 = min(hint, h0 + hchunk);
+        if (h0 < h1) {
+            const size_t head = ((size_t)(blockIdx.z * p.H + blockIdx.y) * p.C + h0) * HD * sizeof(KT);
+            const uint32_t bytes = (uint32_t)(h1 - h0) * HD * (uint32_t)sizeof(KT);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(static_cast<const char*>(p.kcache) + head), "r"(bytes)
+                         : "memory");
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(static_cast<const char*>(p.vcache) + head), "r"(bytes)
+                         : "memory");
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     constexpr int VEC = 16 / sizeof(KT);  // elements per 16-byte load
     constexpr int LPR = HD / VEC;         // lanes per cached row
     constexpr int RPW = 32 / LPR;         // rows per warp per load

@@ -1134,7 +1134,9 @@ static rg_status waits_check(rg_gpt* m) {
     return rg_tc_wait_check(m->ctx);
 }
 
-static rg_status run_steps(rg_gpt* m, size_t steps) {
+// need_logits: the caller reads the full logit rows afterwards.  A tensor-parallel persistent launch leaves every rank
+// with its own vocabulary slice only (the ids are complete), so such a call takes the launch form, which gathers them.
+static rg_status run_steps(rg_gpt* m, size_t steps, bool need_logits = false) {
     const int B = (int)m->curB;
     cudaStream_t s = m->ctx->stream;
     if (rg_cloop_supports(m, B)) {
@@ -1148,7 +1150,7 @@ static rg_status run_steps(rg_gpt* m, size_t steps) {
         // no cluster shape of this GPU fits the model, or the clusters cannot all be resident: the forms below
         // compute the same thing
     }
-    if (rg_mega_supports(m, B)) {
+    if (rg_mega_supports(m, B) && !(m->tp_size > 1 && need_logits)) {
         // one persistent cooperative kernel runs all the steps
         rg_status st = rg_mega_run(m, B, m->pos, steps);
         if (st == RG_OK) {
@@ -1210,7 +1212,7 @@ extern "C" rg_status rg_gpt_decode_step(rg_gpt* m, const uint32_t* tok, float* l
         if (tok[b] >= (uint32_t)m->V)
             return rg_fail(RG_ERR_INVALID_INPUT, "Invalid input: index %u out of bounds for vocabulary size %d", tok[b], m->V);
     RG_CUDA(cudaMemcpy2DAsync(m->tokens + m->pos, (size_t)m->C * 4, tok, 4, 4, B, cudaMemcpyHostToDevice, m->ctx->stream));
-    RG_TRY(run_steps(m, 1));
+    RG_TRY(run_steps(m, 1, logits != nullptr));
     if (logits) RG_CUDA(cudaMemcpyAsync(logits, m->logits, B * (size_t)m->V * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
     if (argmax) RG_CUDA(cudaMemcpyAsync(argmax, m->picks, B * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
     RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
@@ -1298,7 +1300,7 @@ extern "C" rg_status rg_gpt_generate(rg_gpt* m, const uint32_t* prompt, size_t B
             // one step at a time: the draw replaces the greedy pick the step left at the next position
             RG_TRY(sample_rows(m, (int)B, P, temperature, top_k, seed, 0));
             for (size_t i = 1; i < max_new; i++) {
-                RG_TRY(run_steps(m, 1));
+                RG_TRY(run_steps(m, 1, true));
                 RG_TRY(sample_rows(m, (int)B, P + i, temperature, top_k, seed, (unsigned)i));
             }
         }
@@ -1384,8 +1386,11 @@ static rg_status tp_peer_setup(rg_gpt* m) {
     cudaStream_t s = m->ctx->stream;
     const char* mode = getenv("RG_B200_TP_ALLREDUCE");
     int ok = (T <= RG_TP_MAX && !(mode && strcmp(mode, "nccl") == 0)) ? 1 : 0;
-    const size_t words = 2 * (size_t)T * m->Bmax * m->D;
+    const size_t ar_words = 2 * (size_t)T * m->Bmax * m->D;
+    const size_t mega_words = 2 * (size_t)T * 4 * m->D + (size_t)T * m->ctx->sm_count * 4 * 2;  // 4 = sequences a persistent launch takes at most
+    const size_t words = ar_words + mega_words;
     RG_TRY(dalloc(m, (void**)&m->tp_recv, words * 8));
+    m->tp_mega_off = ar_words;
     RG_TRY(dalloc(m, (void**)&m->d_tp_epoch, 16));
     RG_CUDA(cudaMemsetAsync(m->tp_recv, 0, words * 8, s));  // tag 0 never matches: tags start at 1
     RG_CUDA(cudaMemsetAsync(m->d_tp_epoch, 0, 16, s));
@@ -1425,6 +1430,13 @@ static rg_status tp_peer_setup(rg_gpt* m) {
     dfree(m, dh);
     m->tp_fused = all_ok > 0.5f;
     if (!m->tp_fused) tp_peer_close(m);
+    return RG_OK;
+}
+
+rg_status rg_tp_stream_barrier(rg_gpt* m) {
+    if (m->tp_size <= 1 || !m->nccl_comm) return RG_OK;
+    float* word = reinterpret_cast<float*>(m->d_tp_epoch + 3);  // stays 0
+    RG_NCCL(g_nccl.AllReduce(word, word, 1, ncclFloat32, ncclSum, (ncclComm_t)m->nccl_comm, m->ctx->stream));
     return RG_OK;
 }
 

@@ -36,6 +36,9 @@ struct rg_gpt {
     unsigned long long* tp_recv = nullptr;
     unsigned long long* tp_peer[16] = {};
     bool tp_fused = false;
+    // after the all-reduce slots, the same buffer holds the receive regions of the tensor-parallel persistent token loop
+    // (rg_mega.cu): [tp_size][4][D] out-projection partials, the same for FC2, [tp_size][SMs][4][2] picks; in words
+    size_t tp_mega_off = 0;
     unsigned* d_tp_epoch = nullptr;  // token steps enqueued so far (tags)
     int* d_tp_err = nullptr;         // set by a wait that gave up
     size_t pgatherCap = 0;
@@ -94,6 +97,9 @@ rg_status rg_gemm_bf16_tc_parts(rg_ctx* ctx, const void* A16, int M, int K, cons
 // rg_attn_tc.cu: RG_ERR_UNSUPPORTED when the shape is outside the tensor-core attention kernel's limits
 rg_status rg_attn_bf16_tc(rg_ctx* ctx, const float* qkv, const void* kcache, int B, int H, int T, int C, int D, int hd, int causal,
                           void* q16, void* vt16, float* out);
+
+// rg_gpt.cu: a one-element all-reduce on the model's stream (tensor parallel only)
+rg_status rg_tp_stream_barrier(rg_gpt* m);
 
 // rg_mega.cu
 rg_status rg_mega_create(rg_gpt* m);            // after the weights are on the device

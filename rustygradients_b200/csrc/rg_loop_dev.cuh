@@ -148,8 +148,12 @@ __device__ __forceinline__ void mg_ring_release(mg_cons& r) {
     if (++r.slot == r.nslot) r.slot = 0, r.parity ^= 1u;
 }
 
+template <bool SYS = false>
 __device__ __forceinline__ void mg_ld_word2(const mg_word* p, mg_word& a, mg_word& b) {
-    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    if constexpr (SYS)  // words that another GPU stores over NVLink
+        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    else
+        asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
 
 // Fetch one stage input vector of n values (n even) into dst (shared memory) from
@@ -160,7 +164,7 @@ __device__ __forceinline__ void mg_ld_word2(const mg_word* p, mg_word& a, mg_wor
 // read again, after a short pause that keeps the polling traffic of 148 CTAs off the L2.
 // RT = false compiles the wait limit in and leaves the optional pause out (the noinline routines would otherwise read
 // both from the caller's stack inside the polling loop: 3 % of the token time on the GPT-2-small shape).
-template <int U = 8, bool RT = true>
+template <int U = 8, bool RT = true, bool SYS = false>
 __device__ __noinline__ void mg_fetch(const mg_word* src, int n, uint32_t tag, float* dst, mg_ctl& ctl) {
     __builtin_assume(__isShared(dst));
     const int npair = n >> 1;
@@ -174,7 +178,7 @@ __device__ __noinline__ void mg_fetch(const mg_word* src, int n, uint32_t tag, f
             mg_word w[U][2];
 #pragma unroll
             for (int u = 0; u < U; u++)
-                if (pending & (1u << u)) mg_ld_word2(src + 2 * (base + u * MG_THREADS), w[u][0], w[u][1]);
+                if (pending & (1u << u)) mg_ld_word2<SYS>(src + 2 * (base + u * MG_THREADS), w[u][0], w[u][1]);
             uint32_t done = 0;
 #pragma unroll
             for (int u = 0; u < U; u++) {

@@ -37,6 +37,8 @@ enum { MG_QKV = 0, MG_ATTN = 1, MG_OPROJ = 2, MG_FC1 = 3, MG_FC2 = 4, MG_HEAD = 
 enum { MG_FIRST = 1, MG_LAST = 2 };
 
 
+#define MG_TP_MAX 16
+
 struct mg_op {
     int type, layer;
     int nq, q0;  // projection: number of 16-byte column groups and the first one; attention: sequence b and head h
@@ -81,6 +83,15 @@ struct mg_params {
     int withhold_layer;   // test hook: CTA 0 does not publish its q|k|v outputs of this block (-1: off)
     int S;  // CTAs that share one (sequence, head) in the attention stage, each a slice of the context
     float scale;
+    // Tensor parallel: H, F and V above are THIS RANK's heads, hidden columns and vocabulary slice; D is the model
+    // width; Dq = H * hd is the width of each of the q, k, v segments (= D without tensor parallelism).
+    int Dq, XLEN, ldl, v0;  // XLEN: stride of the stage-input vectors (max(D, F)); ldl: row stride of `logits`
+    int tp_rank, tp_size;
+    int n_pick_of[MG_TP_MAX];  // head CTAs of every rank; rank r's picks start at r * pick_stride
+    int pick_stride;
+    mg_word* tp_xc[MG_TP_MAX];    // every rank's receive region of the out-projection partial sums: [tp_size][B][D] words
+    mg_word* tp_xe[MG_TP_MAX];    // ... of the FC2 partial sums
+    mg_word* tp_pick[MG_TP_MAX];  // ... of the picks: [tp_size][pick_stride][B][2]
 };
 
 struct rg_mega {
@@ -265,7 +276,7 @@ __device__ __forceinline__ void mg_group_dots(const mg_op& op, mg_cons& ring, mg
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-template <typename WT, int B, int NQ, bool TRACE>
+template <typename WT, int B, int NQ, bool TRACE, bool TP = false>
 __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(const mg_params p) {
     constexpr int VEC = mg_vec<WT>::N;
     constexpr int KVS = sizeof(WT);  // the KV cache has the weight dtype
@@ -276,7 +287,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x;
-    const int XLEN = p.F;
+    const int XLEN = p.XLEN;
 
     // ---- shared memory carve-up (must match mg_smem_bytes on the host) ----
     unsigned char* sp = smem_raw;
@@ -317,7 +328,20 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
     sp += 4 * 4;
     float* awts = reinterpret_cast<float*>(sp);  // [256] normalised weights of the attention records
     sp += 256 * 4;
-    float* pickbuf = reinterpret_cast<float*>(sp);  // [n_pick_ctas * B * 2]
+    float* pickbuf = reinterpret_cast<float*>(sp);  // [n_pick_ctas * B * 2]; tensor parallel: [tp_size][pick_stride][B][2]
+    sp += ((size_t)(TP ? p.tp_size * p.pick_stride : p.n_pick_ctas) * B * 2 * 4 + 15) & ~(size_t)15;
+    // tensor parallel: the ranks' receive regions and head-CTA counts, copied out of the kernel parameters (a parameter
+    // array indexed by a run-time rank would be copied to local memory by every thread)
+    sp = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(sp) + 15) & ~(uintptr_t)15);
+    mg_word** s_tp = reinterpret_cast<mg_word**>(sp);  // [3][MG_TP_MAX]: out-projection partials, FC2 partials, picks
+    int* s_npick = reinterpret_cast<int*>(sp + 3 * MG_TP_MAX * 8);  // [MG_TP_MAX]
+    if constexpr (TP) {
+        if (tid == 0) {
+#pragma unroll
+            for (int r = 0; r < MG_TP_MAX; r++)
+                s_tp[r] = p.tp_xc[r], s_tp[MG_TP_MAX + r] = p.tp_xe[r], s_tp[2 * MG_TP_MAX + r] = p.tp_pick[r], s_npick[r] = p.n_pick_of[r];
+        }
+    }
     // every one of these is a shared-memory pointer: say so, so that ld.shared / st.shared are emitted (see mg_ring_wait)
     __builtin_assume(__isShared(slots)), __builtin_assume(__isShared(ops)), __builtin_assume(__isShared(cds));
     __builtin_assume(__isShared(xs)), __builtin_assume(__isShared(xemb)), __builtin_assume(__isShared(go));
@@ -454,7 +478,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                 const int arows = max(0, min(pos, r_lo + csz) - r_lo);  // cached rows of this CTA's slice
                 for (int i = tid; i < (is_last ? 3 : 1) * HD; i += MG_THREADS) {
                     const int which = i / HD, d = i - which * HD;
-                    const mg_word* src = p.buf_qkv + (size_t)b * 3 * p.D + which * p.D + h * HD + d;
+                    const mg_word* src = p.buf_qkv + (size_t)b * 3 * p.Dq + which * p.Dq + h * HD + d;
                     uint32_t spins = 0;
                     mg_word w = mg_ld_word(src);
                     while ((uint32_t)(w >> 32) != tag) {
@@ -655,7 +679,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                     const int hshift = 31 - __clz(p.hd);  // head_dim is 32, 64 or 128
 #pragma unroll
                     for (int b = 0; b < B; b++) {
-                        for (int k = tid; k < p.D; k += MG_THREADS) {
+                        for (int k = tid; k < p.Dq; k += MG_THREADS) {
                             const int hh = k >> hshift, d = k & (p.hd - 1);
                             const int wi = (b * p.H + hh) * p.S;
                             const float* r0 = xs + (size_t)wi * rec + 2 + d;
@@ -673,7 +697,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                                 }
                                 o = __fdividef(o, den);
                             }
-                            vec[b * p.D + k] = o;  // element k stays with thread k mod 256: no barrier before the dot products
+                            vec[b * p.Dq + k] = o;  // element k stays with thread k mod 256: no barrier before the dot products
                         }
                     }
                 } else {
@@ -688,7 +712,7 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
             float t0 = 0.f, t1 = 0.f;
             const float* xin = xs;
             int xstride = XLEN;
-            if (op.type == MG_OPROJ) xin = xs + ((B * p.H * p.S * (p.hd + 2) + 3) & ~3), xstride = p.D;
+            if (op.type == MG_OPROJ) xin = xs + ((B * p.H * p.S * (p.hd + 2) + 3) & ~3), xstride = p.Dq;
             __builtin_assume(__isShared(xin));
             if (op.uv == VEC) {
                 switch (op.nq) {
@@ -740,11 +764,41 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                 float s = 0.f;
 #pragma unroll
                 for (int w2 = 0; w2 < NWARP; w2++) s += red[w2 * nv + tid];
-                s = ln_stage ? fmaf(rstd[b], fmaf(-mu[b], t1, s), t0) : s + t0;
                 const int col = op.q0 * op.uv + jq;
+                if constexpr (TP) {
+                    // Row-split stages (out-projection, FC2): this rank holds a partial sum.  It goes, tagged, into
+                    // every rank's receive region (plain stores, NVLink for the peers); then the same thread collects
+                    // the tp_size partials of ITS element from its own region and adds them in rank order, so every
+                    // rank computes the same bits.  Bias and residual are added once, after the sum.
+                    if (op.type == MG_OPROJ || op.type == MG_FC2) {
+                        mg_word* const* regs = s_tp + (op.type == MG_OPROJ ? 0 : MG_TP_MAX);
+                        const size_t slot = ((size_t)p.tp_rank * B + b) * p.D + col;
+                        const mg_word mine = ((mg_word)tag << 32) | __float_as_uint(s);
+                        for (int r = 0; r < p.tp_size; r++)
+                            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(regs[r] + slot), "l"(mine) : "memory");
+                        const mg_word* own = regs[p.tp_rank] + (size_t)b * p.D + col;
+                        float sum = 0.f;
+                        for (int r = 0; r < p.tp_size && !ctl.dead; r++) {
+                            const mg_word* src = own + (size_t)r * B * p.D;
+                            uint32_t spins = 0;
+                            mg_word w;
+                            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
+                            while ((uint32_t)(w >> 32) != tag) {
+                                if (++spins > ctl.limit || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
+                                    mg_give_up(ctl);
+                                    break;
+                                }
+                                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
+                            }
+                            sum += __uint_as_float((uint32_t)w);
+                        }
+                        s = sum;
+                    }
+                }
+                s = ln_stage ? fmaf(rstd[b], fmaf(-mu[b], t1, s), t0) : s + t0;
                 if (op.type == MG_QKV) {
                     if (!(TRACE && cta == 0 && op.layer == p.withhold_layer))
-                        mg_st_word(p.buf_qkv + (size_t)b * 3 * p.D + col, tag, __float_as_uint(s));
+                        mg_st_word(p.buf_qkv + (size_t)b * 3 * p.Dq + col, tag, __float_as_uint(s));
                 } else if (op.type == MG_OPROJ) {
                     const float v = xres[b * p.res_cap + op.aux + jq] + s;
                     xres[b * p.res_cap + op.aux + jq] = v;
@@ -757,8 +811,9 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                     xres[b * p.res_cap + op.aux + jq] = v;
                     mg_st_word(p.buf_xe + (size_t)b * p.D + col, tag, __float_as_uint(v));
                 } else if (col < p.V) {  // MG_HEAD
-                    p.logits[(size_t)b * p.V + col] = s;
-                    if (s > my_best || (s == my_best && col < my_besti)) my_best = s, my_besti = col;
+                    p.logits[(size_t)b * p.ldl + col] = s;
+                    const int id = p.v0 + col;
+                    if (s > my_best || (s == my_best && id < my_besti)) my_best = s, my_besti = id;
                 }
             }
             if (tracing) tr[3] = mg_globaltimer(), tr[4] = (unsigned long long)wait_cyc, tr[5] = (unsigned long long)poll_cyc;
@@ -775,9 +830,19 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                         const int ix = besti[i];
                         if (v > bv || (v == bv && ix < bi)) bv = v, bi = ix;
                     }
-                    mg_word* dst = p.buf_pick + ((size_t)op.aux * B + tid) * 2;
-                    mg_st_word(dst, tagbase + (uint32_t)p.L + 1u, __float_as_uint(bv));
-                    mg_st_word(dst + 1, tagbase + (uint32_t)p.L + 1u, (uint32_t)bi);
+                    const uint32_t ptag = tagbase + (uint32_t)p.L + 1u;
+                    if constexpr (TP) {  // every rank needs every rank's candidates
+                        const size_t slot = (((size_t)p.tp_rank * p.pick_stride + op.aux) * B + tid) * 2;
+                        const mg_word w0 = ((mg_word)ptag << 32) | __float_as_uint(bv), w1 = ((mg_word)ptag << 32) | (uint32_t)bi;
+                        for (int r = 0; r < p.tp_size; r++) {
+                            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(s_tp[2 * MG_TP_MAX + r] + slot), "l"(w0) : "memory");
+                            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(s_tp[2 * MG_TP_MAX + r] + slot + 1), "l"(w1) : "memory");
+                        }
+                    } else {
+                        mg_word* dst = p.buf_pick + ((size_t)op.aux * B + tid) * 2;
+                        mg_st_word(dst, ptag, __float_as_uint(bv));
+                        mg_st_word(dst + 1, ptag, (uint32_t)bi);
+                    }
                 }
             }
         }
@@ -785,7 +850,13 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
         flush_append();
 
         // ---- greedy pick (top_k = 1 of src/wasm_api.rs:120-156): best over all CTAs, lowest index on ties ----
-        mg_fetch<8, TRACE>(p.buf_pick, p.n_pick_ctas * B * 2, tagbase + (uint32_t)p.L + 1u, pickbuf, ctl);
+        if constexpr (TP) {
+            for (int r = 0; r < p.tp_size; r++)
+                mg_fetch<8, TRACE, true>(s_tp[2 * MG_TP_MAX + p.tp_rank] + (size_t)r * p.pick_stride * B * 2, s_npick[r] * B * 2,
+                                         tagbase + (uint32_t)p.L + 1u, pickbuf + (size_t)r * p.pick_stride * B * 2, ctl);
+        } else {
+            mg_fetch<8, TRACE>(p.buf_pick, p.n_pick_ctas * B * 2, tagbase + (uint32_t)p.L + 1u, pickbuf, ctl);
+        }
         // everything any CTA stored before its pick (cache rows included) is ordered before what follows here
         __threadfence();
         mg_fence_proxy_async();
@@ -793,10 +864,14 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
         if (warp < B) {  // warp b scans the candidates of sequence b
             float bv = -INFINITY;
             int bi = 0x7fffffff;
-            for (int r = lane; r < p.n_pick_ctas; r += 32) {
-                const float v = pickbuf[(r * B + warp) * 2];
-                const int ix = (int)__float_as_uint(pickbuf[(r * B + warp) * 2 + 1]);
-                if (v > bv || (v == bv && ix < bi)) bv = v, bi = ix;
+            for (int rk = 0; rk < (TP ? p.tp_size : 1); rk++) {
+                const float* pb = pickbuf + (size_t)rk * p.pick_stride * B * 2;
+                const int n = TP ? s_npick[rk] : p.n_pick_ctas;
+                for (int r = lane; r < n; r += 32) {
+                    const float v = pb[(r * B + warp) * 2];
+                    const int ix = (int)__float_as_uint(pb[(r * B + warp) * 2 + 1]);
+                    if (v > bv || (v == bv && ix < bi)) bv = v, bi = ix;
+                }
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
@@ -894,8 +969,9 @@ static size_t mg_smem_bytes(const rg_gpt* m, int B, int NQ, int nslot, int max_o
     const int VEC = m->bf16 ? 8 : 4;
     const int NOUT = B * NQ * VEC;
     size_t s = (size_t)nslot * MG_SLOT_BYTES + 128 + (size_t)max_ops * sizeof(mg_op) + (size_t)max_cd * sizeof(mg_cdesc);
-    s += (size_t)B * m->F * 4 + (size_t)B * m->D * 4 + (size_t)B * res_cap * 4 + (size_t)MG_THREADS * VEC * 4 + 128 * 4 + 3 * 128 * 4;
-    s += 2 * 8 * (size_t)NOUT * 4 + 2 * 8 * 4 * MG_BMAX * 4 + 2 * (size_t)NOUT * 4 + MG_BMAX * 4 + 16 + 256 * 4 + (size_t)n_pick * B * 2 * 4;
+    s += (size_t)B * std::max(m->D, m->Fl) * 4 + (size_t)B * m->D * 4 + (size_t)B * res_cap * 4 + (size_t)MG_THREADS * VEC * 4 + 128 * 4 + 3 * 128 * 4;
+    s += 2 * 8 * (size_t)NOUT * 4 + 2 * 8 * 4 * MG_BMAX * 4 + 2 * (size_t)NOUT * 4 + MG_BMAX * 4 + 16 + 256 * 4 + (((size_t)n_pick * B * 2 * 4 + 15) & ~(size_t)15);
+    s += 16 + 3 * MG_TP_MAX * 8 + MG_TP_MAX * 4;  // tensor parallel: pointer table and head-CTA counts
     return s + 128;
 }
 
@@ -905,10 +981,12 @@ static void mg_build_program(rg_gpt* m, rg_mega* g, int B) {
     std::vector<std::vector<mg_op>> per(G);
     // slices of the context per (sequence, head): as many as there are CTAs for, at most 4, and only as many as
     // let the out-projection stage hold all attention records plus its input vectors in the xs/xemb/go overlay
-    g->S = std::max(1, std::min(4, G / std::max(1, B * m->H)));
+    // (a tensor-parallel rank builds the program of its own shard: Hl heads, Fl hidden columns, Vl vocabulary entries)
+    const int H = m->Hl, Dq = m->Dl, F = m->Fl, XL = std::max(m->D, m->Fl);
+    g->S = std::max(1, std::min(4, G / std::max(1, B * H)));
     if (const char* e = getenv("RG_B200_ATTN_SLICES")) g->S = std::max(1, std::min(g->S, atoi(e)));  // experiments: fewer slices
-    while (g->S > 1 && (size_t)B * m->H * g->S * (m->hd + 2) + 4 + (size_t)B * m->D >
-                           (size_t)B * m->F + (size_t)B * m->D + (size_t)MG_THREADS * VEC)
+    while (g->S > 1 && (size_t)B * H * g->S * (m->hd + 2) + 4 + (size_t)B * Dq >
+                           (size_t)B * XL + (size_t)B * m->D + (size_t)MG_THREADS * VEC)
         g->S--;
     int rot = 0;
     auto add_projection = [&](int type, int layer, int K, int N, int fixed_rot, int ub) {
@@ -956,20 +1034,20 @@ static void mg_build_program(rg_gpt* m, rg_mega* g, int B) {
     const int extraD = rg_cdiv(m->D, VEC / 2) % G;
     rot = extraD;  // stages with N != D put their larger shares on other CTAs than the N = D stages do
     for (int l = 0; l < m->L; l++) {
-        add_projection(MG_QKV, l, m->D, 3 * m->D, -1, 16);
-        for (int pr = 0; pr < B * m->H * g->S; pr++) {  // one CTA per (sequence, head, slice), from the top of the grid down
+        add_projection(MG_QKV, l, m->D, 3 * Dq, -1, 16);
+        for (int pr = 0; pr < B * H * g->S; pr++) {  // one CTA per (sequence, head, slice), from the top of the grid down
             mg_op op;
             memset(&op, 0, sizeof(op));
             const int bh = pr / g->S;
-            op.type = MG_ATTN, op.layer = l, op.nq = bh / m->H, op.q0 = bh % m->H, op.aux = pr % g->S, op.K = g->S;
+            op.type = MG_ATTN, op.layer = l, op.nq = bh / H, op.q0 = bh % H, op.aux = pr % g->S, op.K = g->S;
             op.flags = MG_FIRST | MG_LAST;
             per[(G - 1) - (pr % G)].push_back(op);
         }
-        add_projection(MG_OPROJ, l, m->D, m->D, 0, 8);
-        add_projection(MG_FC1, l, m->D, m->F, -1, 16);
-        add_projection(MG_FC2, l, m->F, m->D, 0, 8);
+        add_projection(MG_OPROJ, l, Dq, m->D, 0, 8);
+        add_projection(MG_FC1, l, m->D, F, -1, 16);
+        add_projection(MG_FC2, l, F, m->D, 0, 8);
     }
-    g->n_pick_ctas = add_projection(MG_HEAD, m->L, m->D, m->V, -1, 16);
+    g->n_pick_ctas = add_projection(MG_HEAD, m->L, m->D, m->Vl, -1, 16);
     g->ops.clear();
     g->cta_off.assign(G + 1, 0);
     g->max_ops = 1;
@@ -1037,9 +1115,9 @@ static void mg_pack_all(rg_gpt* m, rg_mega* g) {
     m->ctx->launches += 4 * m->L + 1;
 }
 
-template <typename WT, int B, int NQ, bool TRACE>
+template <typename WT, int B, int NQ, bool TRACE, bool TP = false>
 static cudaError_t mg_launch_t(rg_gpt* m, rg_mega* g, mg_params& prm) {
-    auto kern = rg_token_loop_kernel<WT, B, NQ, TRACE>;
+    auto kern = rg_token_loop_kernel<WT, B, NQ, TRACE, TP>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g->smem_bytes);
     if (e != cudaSuccess) return e;
     void* args[] = {&prm};
@@ -1050,6 +1128,8 @@ template <typename WT, int B, int NQ>
 static cudaError_t mg_launch(rg_gpt* m, rg_mega* g, mg_params& prm) {
     // the instrumented build is also the one that honours a lowered wait limit and the withheld signal of the tests
     const bool instrumented = prm.trace || prm.spin_limit != MG_SPIN_LIMIT || prm.withhold_layer != -1 || prm.poll_sleep;
+    // tensor parallel: one instance, with the run-time wait limit (NVLink latency, not instruction count, bounds its stages)
+    if (prm.tp_size > 1) return mg_launch_t<WT, B, NQ, true, true>(m, g, prm);
     return instrumented ? mg_launch_t<WT, B, NQ, true>(m, g, prm) : mg_launch_t<WT, B, NQ, false>(m, g, prm);
 }
 
@@ -1063,10 +1143,10 @@ static cudaError_t mg_launch(rg_gpt* m, rg_mega* g, mg_params& prm) {
 // Every exchange vector (q|k|v, attention records, x after the out-projection, hidden, x after FC2, picks) has its
 // own region with room for MG_PLACE_CANDIDATES positions; cand[i] selects the position of vector i.
 static void mg_exchange_sizes(const rg_gpt* m, const rg_mega* g, int B, size_t (&sz)[MG_PLACE_BUFS]) {
-    sz[0] = (size_t)B * 3 * m->D;
-    sz[1] = (size_t)B * m->H * g->S * (m->hd + 2);
+    sz[0] = (size_t)B * 3 * m->Dl;
+    sz[1] = (size_t)B * m->Hl * g->S * (m->hd + 2);
     sz[2] = (size_t)B * m->D;
-    sz[3] = (size_t)B * m->F;
+    sz[3] = (size_t)B * m->Fl;
     sz[4] = (size_t)B * m->D;
     sz[5] = (size_t)g->n_pick_ctas * B * 2;
 }
@@ -1094,7 +1174,7 @@ static rg_status mg_prepare(rg_gpt* m, int B) {
     // ring depth: as many 32 KB slots as fit beside the rest (at most 6)
     g->nslot = 0;
     for (int ns = 6; ns >= 2; ns--) {
-        const size_t need = mg_smem_bytes(m, B, NQ, ns, g->max_ops, g->max_cd, g->res_cap, g->n_pick_ctas);
+        const size_t need = mg_smem_bytes(m, B, NQ, ns, g->max_ops, g->max_cd, g->res_cap, m->tp_size > 1 ? m->tp_size * g->G : g->n_pick_ctas);
         if (need <= 227 * 1024) {
             g->nslot = ns;
             g->smem_bytes = need;
@@ -1120,10 +1200,12 @@ static rg_status mg_prepare(rg_gpt* m, int B) {
     g->buf_bytes = words * 8;
     for (int& c : g->place) c = 0;
     mg_set_exchange(m, g, B, g->place);
-    g->placed = false;
+    g->placed = m->tp_size > 1;  // (tensor parallel: no placement runs, they would have to be agreed between the ranks)
     RG_CUDA(cudaMemset(g->buf_base, 0, g->buf_bytes));
     RG_CUDA(cudaMemset(g->d_abort, 0, 16));
-    m->epoch = 0;
+    // Tags restart with the local buffers.  Not so across ranks: the peers' words in this rank's receive regions keep
+    // their tags, so a tensor-parallel model never reuses a tag (all ranks count the same steps).
+    if (m->tp_size == 1) m->epoch = 0;
     RG_CUDA(cudaMemcpy(g->d_ops, g->ops.data(), g->ops.size() * sizeof(mg_op), cudaMemcpyHostToDevice));
     RG_CUDA(cudaMemcpy(g->d_cta_off, g->cta_off.data(), (g->G + 1) * sizeof(int), cudaMemcpyHostToDevice));
     RG_CUDA(cudaMemcpy(g->d_cds, g->cds.data(), g->cds.size() * sizeof(mg_cdesc), cudaMemcpyHostToDevice));
@@ -1137,7 +1219,8 @@ static rg_status mg_prepare(rg_gpt* m, int B) {
 }
 
 bool rg_mega_supports(const rg_gpt* m, int B) {
-    return m->mega != nullptr && m->use_mega && m->cfg.causal && m->tp_size == 1 && mg_variant(B) >= 0 && m->hd <= 128;
+    if (m->tp_size > 1 && !(m->tp_fused && m->tp_mega_off != 0 && B <= MG_BMAX)) return false;  // needs the peer-mapped regions
+    return m->mega != nullptr && m->use_mega && m->cfg.causal && mg_variant(B) >= 0 && m->hd <= 128;
 }
 
 rg_status rg_mega_create(rg_gpt* m) {
@@ -1168,6 +1251,10 @@ static rg_status mg_run_once(rg_gpt* m, int B, size_t pos0, size_t n_steps) {
     rg_mega* g = m->mega;
     // tags are (epoch * (L+1) + layer + 1) in 32 bits: start over long before they wrap
     if (((uint64_t)m->epoch + n_steps + 1) * (uint64_t)(m->L + 1) >= 0xfffffff0ull) {
+        if (m->tp_size > 1) {  // cannot clear the peers' words from here: the launch form takes over
+            m->use_mega = false;
+            return RG_ERR_UNSUPPORTED;
+        }
         RG_CUDA(cudaStreamSynchronize(m->ctx->stream));
         RG_CUDA(cudaMemset(g->buf_base, 0, g->buf_bytes));
         m->epoch = 0;
@@ -1181,9 +1268,24 @@ static rg_status mg_run_once(rg_gpt* m, int B, size_t pos0, size_t n_steps) {
     prm.kc = (unsigned char*)m->kc, prm.vc = (unsigned char*)m->vc, prm.kv_layer_bytes = m->kv_layer_bytes;
     prm.buf_qkv = g->buf_qkv, prm.buf_a = g->buf_a, prm.buf_xc = g->buf_xc, prm.buf_h = g->buf_h, prm.buf_xe = g->buf_xe;
     prm.buf_pick = g->buf_pick;
-    prm.logits = m->logits, prm.tokens = m->tokens, prm.picks = m->picks, prm.d_pos = m->d_pos, prm.d_pos_next = m->d_pos_next;
+    prm.logits = m->logits + m->v0, prm.tokens = m->tokens, prm.picks = m->picks, prm.d_pos = m->d_pos, prm.d_pos_next = m->d_pos_next;
     prm.abort_flag = g->d_abort;
-    prm.V = m->V, prm.D = m->D, prm.L = m->L, prm.H = m->H, prm.hd = m->hd, prm.C = m->C, prm.F = m->F;
+    prm.V = m->Vl, prm.D = m->D, prm.L = m->L, prm.H = m->Hl, prm.hd = m->hd, prm.C = m->C, prm.F = m->Fl;
+    prm.Dq = m->Dl, prm.XLEN = std::max(m->D, m->Fl), prm.ldl = m->V, prm.v0 = m->v0;
+    prm.tp_rank = m->tp_rank, prm.tp_size = m->tp_size, prm.pick_stride = g->G;
+    if (m->tp_size > 1) {
+        // the peers' regions inside every rank's receive buffer (rg_gpt.cu lays them out: see rg_tp_mega_words)
+        const size_t xwords = (size_t)m->tp_size * MG_BMAX * m->D;
+        for (int r = 0; r < m->tp_size; r++) {
+            mg_word* base = reinterpret_cast<mg_word*>(m->tp_peer[r]) + m->tp_mega_off;
+            prm.tp_xc[r] = base, prm.tp_xe[r] = base + xwords, prm.tp_pick[r] = base + 2 * xwords;
+            // head CTAs of rank r: what add_projection(MG_HEAD) gives for its vocabulary slice
+            const int v0r = std::min(m->V, r * m->Vpad), vlr = std::max(0, std::min(m->Vpad, m->V - v0r));
+            prm.n_pick_of[r] = std::min(g->G, rg_cdiv(vlr, 16 / (int)m->wsize));
+        }
+    } else {
+        prm.n_pick_of[0] = g->n_pick_ctas;
+    }
     prm.act = m->cfg.activation;
     prm.pos0 = (int)pos0, prm.n_steps = (int)n_steps, prm.epoch0 = m->epoch;
     prm.S = g->S;
@@ -1281,6 +1383,9 @@ rg_status rg_mega_run(rg_gpt* m, int B, size_t pos0, size_t n_steps) {
         st = mg_place_exchange(m, B, pos0);
         if (st != RG_OK) return st;  // RG_ERR_UNSUPPORTED included: the caller falls back to the graph step
     }
+    // tensor parallel: the ranks' kernels wait for each other's words, so they should start together; a small collective
+    // on the stream, after this rank's (possibly long) preparation, lines the launches up
+    if (m->tp_size > 1) RG_TRY(rg_tp_stream_barrier(m));
     return mg_run_once(m, B, pos0, n_steps);
 }
 
@@ -1292,7 +1397,8 @@ rg_status rg_mega_check(rg_gpt* m) {
     if (flag) {
         cudaMemsetAsync(m->mega->d_abort, 0, sizeof(int), m->ctx->stream);
         cudaMemsetAsync(m->mega->buf_base, 0, m->mega->buf_bytes, m->ctx->stream);
-        m->epoch = 0;
+        if (m->tp_size == 1) m->epoch = 0;
+        else m->use_mega = false;  // the ranks may no longer agree on the step count: the launch form from now on
         return rg_fail(RG_ERR_TIMEOUT, "a bounded wait inside the persistent token-loop kernel gave up; the step was abandoned");
     }
     return RG_OK;
