@@ -367,9 +367,17 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     model.close()
     extra = {}
     if not args.no_extra:
-        extra["batched"] = run_batched(torch, rg, O, be, dev, stream, barrier, rank, world)
+        # the headline above is complete at this point: a failure in an extra record is reported inside that record
+        # instead of taking the whole line down (a failure that hits every rank alike, e.g. a wait that ran out)
+        try:
+            extra["batched"] = run_batched(torch, rg, O, be, dev, stream, barrier, rank, world)
+        except rg.RustyGradientsError as e:
+            extra["batched"] = {"error": f"{type(e).__name__}: {e}"}
         if world > 1:
-            extra["tp"] = run_tp(torch, rg, be, dev, stream, barrier, rank, world)
+            try:
+                extra["tp"] = run_tp(torch, rg, be, dev, stream, barrier, rank, world)
+            except rg.RustyGradientsError as e:
+                extra["tp"] = {"error": f"{type(e).__name__}: {e}"}
 
     if rank == 0:
         tokens = world * B * G * args.steps

@@ -273,6 +273,53 @@ __device__ __forceinline__ void mg_group_dots(const mg_op& op, mg_cons& ring, mg
     }
 }
 
+// Tensor parallel, row-split stages (out-projection, FC2): a rank holds a partial sum of element `elem`.  It goes,
+// tagged, into every rank's receive region; then the same thread collects the tp_size partials of ITS element from its
+// own region (`stride` words apart) and adds them in rank order, so every rank computes the same bits.  All words are
+// requested together; only those not valid yet are read again.
+// Bounded like every wait of the kernel.  Kept out of line: its 16 words in flight would otherwise cost the token loop
+// registers it does not have.
+__device__ __noinline__ float mg_tp_reduce(mg_word* const* regs, int rank, int T, size_t stride, size_t elem, uint32_t tag, float part,
+                                           mg_ctl& ctl) {
+    // this rank's partial sum, tagged, into slot [rank][elem] of every rank's region (plain stores; NVLink for the peers)
+    const mg_word mine = ((mg_word)tag << 32) | __float_as_uint(part);
+    for (int r = 0; r < T; r++)
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(regs[r] + (size_t)rank * stride + elem), "l"(mine) : "memory");
+    const mg_word* own = regs[rank] + elem;
+    float vals[MG_TP_MAX];
+    uint32_t pending = (1u << T) - 1u, spins = 0;
+    while (pending != 0) {
+        mg_word w[MG_TP_MAX];
+#pragma unroll
+        for (int r = 0; r < MG_TP_MAX; r++)
+            if (pending & (1u << r))
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w[r]) : "l"(own + (size_t)r * stride) : "memory");
+#pragma unroll
+        for (int r = 0; r < MG_TP_MAX; r++)
+            if ((pending & (1u << r)) && (uint32_t)(w[r] >> 32) == tag) {
+                vals[r] = __uint_as_float((uint32_t)w[r]);
+                pending &= ~(1u << r);
+            }
+        if (pending != 0 && (++spins > ctl.limit || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag)))) {
+            mg_give_up(ctl);
+            break;
+        }
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int r = 0; r < MG_TP_MAX; r++)
+        if (r < T) sum += (pending & (1u << r)) ? 0.f : vals[r];
+    return sum;
+}
+
+__device__ __noinline__ void mg_tp_publish_pick(mg_word* const* regs, int T, size_t slot, uint32_t tag, float best, int id) {
+    const mg_word w0 = ((mg_word)tag << 32) | __float_as_uint(best), w1 = ((mg_word)tag << 32) | (uint32_t)id;
+    for (int r = 0; r < T; r++) {
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(regs[r] + slot), "l"(w0) : "memory");
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(regs[r] + slot + 1), "l"(w1) : "memory");
+    }
+}
+
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
@@ -771,28 +818,8 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                     // the tp_size partials of ITS element from its own region and adds them in rank order, so every
                     // rank computes the same bits.  Bias and residual are added once, after the sum.
                     if (op.type == MG_OPROJ || op.type == MG_FC2) {
-                        mg_word* const* regs = s_tp + (op.type == MG_OPROJ ? 0 : MG_TP_MAX);
-                        const size_t slot = ((size_t)p.tp_rank * B + b) * p.D + col;
-                        const mg_word mine = ((mg_word)tag << 32) | __float_as_uint(s);
-                        for (int r = 0; r < p.tp_size; r++)
-                            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(regs[r] + slot), "l"(mine) : "memory");
-                        const mg_word* own = regs[p.tp_rank] + (size_t)b * p.D + col;
-                        float sum = 0.f;
-                        for (int r = 0; r < p.tp_size && !ctl.dead; r++) {
-                            const mg_word* src = own + (size_t)r * B * p.D;
-                            uint32_t spins = 0;
-                            mg_word w;
-                            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
-                            while ((uint32_t)(w >> 32) != tag) {
-                                if (++spins > ctl.limit || ((spins & 255u) == 0 && mg_ld_flag(ctl.abort_flag))) {
-                                    mg_give_up(ctl);
-                                    break;
-                                }
-                                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
-                            }
-                            sum += __uint_as_float((uint32_t)w);
-                        }
-                        s = sum;
+                        s = mg_tp_reduce(s_tp + (op.type == MG_OPROJ ? 0 : MG_TP_MAX), p.tp_rank, p.tp_size, (size_t)B * p.D,
+                                         (size_t)b * p.D + col, tag, s, ctl);
                     }
                 }
                 s = ln_stage ? fmaf(rstd[b], fmaf(-mu[b], t1, s), t0) : s + t0;
@@ -832,12 +859,8 @@ __global__ void __launch_bounds__(MG_TOTAL_THREADS, 1) rg_token_loop_kernel(cons
                     }
                     const uint32_t ptag = tagbase + (uint32_t)p.L + 1u;
                     if constexpr (TP) {  // every rank needs every rank's candidates
-                        const size_t slot = (((size_t)p.tp_rank * p.pick_stride + op.aux) * B + tid) * 2;
-                        const mg_word w0 = ((mg_word)ptag << 32) | __float_as_uint(bv), w1 = ((mg_word)ptag << 32) | (uint32_t)bi;
-                        for (int r = 0; r < p.tp_size; r++) {
-                            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(s_tp[2 * MG_TP_MAX + r] + slot), "l"(w0) : "memory");
-                            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(s_tp[2 * MG_TP_MAX + r] + slot + 1), "l"(w1) : "memory");
-                        }
+                        mg_tp_publish_pick(s_tp + 2 * MG_TP_MAX, p.tp_size, (((size_t)p.tp_rank * p.pick_stride + op.aux) * B + tid) * 2, ptag,
+                                           bv, bi);
                     } else {
                         mg_word* dst = p.buf_pick + ((size_t)op.aux * B + tid) * 2;
                         mg_st_word(dst, ptag, __float_as_uint(bv));
