@@ -243,6 +243,9 @@ struct rg_attn_step_args {
     float scale;
 };
 
+#ifndef RG_ATTN_STEP_UNROLL
+#define RG_ATTN_STEP_UNROLL 2
+#endif
 template <typename KT, int HD>
 __global__ void __launch_bounds__(128) rg_attn_step_kernel(rg_attn_step_args p) {
     // Inside a launch chain this kernel may start while the QKV projection before it still runs.  The cached rows it
@@ -326,33 +329,43 @@ __global__ void __launch_bounds__(128) rg_attn_step_kernel(rg_attn_step_args p) 
 #pragma unroll
     for (int j = 0; j < VEC; j++) acc[j] = 0.f;
 
-    for (int tb = t0 + warp * RPW; tb < t1; tb += 4 * RPW) {
-        const int t = tb + grp;
-        const bool ok = t < t1;
-        float kf[VEC], vf[VEC];
-        if (ok && t != pos) {
-            rg_wvec<KT>::load(kc + (size_t)t * HD + sub * VEC, kf);
-            rg_wvec<KT>::load(vc + (size_t)t * HD + sub * VEC, vf);
-        } else {
+    // Several row groups per trip: all 16-byte loads of a trip are issued before anything is computed on them, which
+    // multiplies the bytes a thread keeps in flight (the loop is bound by the latency of these loads, not by arithmetic).
+    constexpr int UNR = RG_ATTN_STEP_UNROLL;
+    for (int tb = t0 + warp * RPW; tb < t1; tb += UNR * 4 * RPW) {
+        float kf[UNR][VEC], vf[UNR][VEC];
+        bool okk[UNR];
 #pragma unroll
-            for (int j = 0; j < VEC; j++) {
-                kf[j] = ok ? sk[sub * VEC + j] : 0.f;
-                vf[j] = ok ? sv[sub * VEC + j] : 0.f;
+        for (int u = 0; u < UNR; u++) {
+            const int t = tb + u * 4 * RPW + grp;
+            okk[u] = t < t1;
+            if (okk[u] && t != pos) {
+                rg_wvec<KT>::load(kc + (size_t)t * HD + sub * VEC, kf[u]);
+                rg_wvec<KT>::load(vc + (size_t)t * HD + sub * VEC, vf[u]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < VEC; j++) {
+                    kf[u][j] = okk[u] ? sk[sub * VEC + j] : 0.f;
+                    vf[u][j] = okk[u] ? sv[sub * VEC + j] : 0.f;
+                }
             }
         }
-        float dot = 0.f;
 #pragma unroll
-        for (int j = 0; j < VEC; j++) dot = fmaf(qf[j], kf[j], dot);
+        for (int u = 0; u < UNR; u++) {
+            float dot = 0.f;
 #pragma unroll
-        for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(RG_FULL_MASK, dot, o);
-        if (ok) {
-            const float sc = dot * p.scale;
-            const float mn = fmaxf(m, sc);
-            const float corr = __expf(m - mn), pr = __expf(sc - mn);
-            l = l * corr + pr;
+            for (int j = 0; j < VEC; j++) dot = fmaf(qf[j], kf[u][j], dot);
 #pragma unroll
-            for (int j = 0; j < VEC; j++) acc[j] = acc[j] * corr + pr * vf[j];
-            m = mn;
+            for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(RG_FULL_MASK, dot, o);
+            if (okk[u]) {
+                const float sc = dot * p.scale;
+                const float mn = fmaxf(m, sc);
+                const float corr = __expf(m - mn), pr = __expf(sc - mn);
+                l = l * corr + pr;
+#pragma unroll
+                for (int j = 0; j < VEC; j++) acc[j] = acc[j] * corr + pr * vf[u][j];
+                m = mn;
+            }
         }
     }
     // merge the lane groups of the CTA in fixed order
