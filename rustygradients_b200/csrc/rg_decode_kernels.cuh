@@ -241,6 +241,10 @@ struct rg_attn_step_args {
     const int* pos;
     int B, H, C, D, NS;
     float scale;
+    // With one slice per (sequence, head) the merge of slices is a division: when this is set (and NS == 1) the kernel
+    // writes the finished head outputs o / l as bf16 rows [B][H * hd], the input of the out-projection, itself
+    // (the same bits rg_attn_merge_kernel would produce from the record).
+    __nv_bfloat16* out16 = nullptr;
 };
 
 #ifndef RG_ATTN_STEP_UNROLL
@@ -376,11 +380,17 @@ __global__ void __launch_bounds__(128) rg_attn_step_kernel(rg_attn_step_args p) 
     __syncthreads();
     float M = -INFINITY;
     for (int i = 0; i < NG; i++) M = fmaxf(M, gm[i]);
+    const bool finish = p.out16 != nullptr && p.NS == 1;
+    float Lall = 0.f;
+    if (finish)
+        for (int i = 0; i < NG; i++)
+            if (gm[i] != -INFINITY) Lall += __expf(gm[i] - M) * gl[i];
     for (int d = tid; d < HD; d += 128) {
         float o = 0.f;
         for (int i = 0; i < NG; i++)
             if (gm[i] != -INFINITY) o += __expf(gm[i] - M) * go[i][d];
         out[2 + d] = o;
+        if (finish) p.out16[(size_t)(b * p.H + h) * HD + d] = __float2bfloat16_rn(o / Lall);
     }
     if (tid == 0) {
         float L = 0.f;
@@ -419,12 +429,13 @@ static __global__ void __launch_bounds__(1024) rg_pick_kernel(rg_pick_args p) {
     const size_t stride = (size_t)p.B * p.V;
     // finished logits in place (one part, no bias): nothing to add and nothing to store, only the scan
     const bool in_place = p.nparts == 1 && !p.bias && p.parts == p.logits;
-    // 4 elements per thread and trip, their loads issued together (a load -> compare chain per element would cost one
-    // memory latency each: V / 1024 = 49 of them for the full vocabulary)
-    for (int v0 = tid; v0 < p.V; v0 += 4 * blockDim.x) {
-        float x[4];
+    // PU elements per thread and trip, their loads issued together (a load -> compare chain per element would cost one
+    // memory latency each: V / 1024 = 49 of them for the full vocabulary; 16 at a time leaves 4 trips)
+    constexpr int PU = 16;
+    for (int v0 = tid; v0 < p.V; v0 += PU * blockDim.x) {
+        float x[PU];
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < PU; u++) {
             const int v = v0 + u * blockDim.x;
             x[u] = -INFINITY;
             if (v < p.V) {
@@ -433,7 +444,7 @@ static __global__ void __launch_bounds__(1024) rg_pick_kernel(rg_pick_args p) {
             }
         }
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < PU; u++) {
             const int v = v0 + u * blockDim.x;
             if (v < p.V) {
                 if (!in_place) p.logits[(size_t)b * p.V + v] = x[u];

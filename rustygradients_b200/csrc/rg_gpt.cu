@@ -1090,13 +1090,17 @@ static int enqueue_step_rows_tc(rg_gpt* m, int B) {
             a.ap = m->ap, a.pos = m->d_pos;
             a.B = B, a.H = m->Hl, a.C = m->C, a.D = m->Dl, a.NS = NS;
             a.scale = 1.f / sqrtf((float)m->hd);
+            if (NS == 1) a.out16 = a16;  // one slice per (sequence, head): the attention kernel finishes the rows itself
             dim3 grid(NS, m->Hl, B);
             if (m->hd == 32) rg_launch(pdl, rg_attn_step_kernel<__nv_bfloat16, 32>, grid, dim3(128), 0, s, a);
             else if (m->hd == 64) rg_launch(pdl, rg_attn_step_kernel<__nv_bfloat16, 64>, grid, dim3(128), 0, s, a);
             else rg_launch(pdl, rg_attn_step_kernel<__nv_bfloat16, 128>, grid, dim3(128), 0, s, a);
-            rg_launch(pdl, rg_attn_merge_kernel, dim3(rg_cdiv(B * D, 256)), dim3(256), 0, s, (const float*)m->ap, (float*)nullptr, B,
-                      m->Hl, m->hd, NS, a16);
-            m->ctx->launches += 2;
+            m->ctx->launches += 1;
+            if (NS > 1) {
+                rg_launch(pdl, rg_attn_merge_kernel, dim3(rg_cdiv(B * D, 256)), dim3(256), 0, s, (const float*)m->ap, (float*)nullptr, B,
+                          m->Hl, m->hd, NS, a16);
+                m->ctx->launches += 1;
+            }
         }
         if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, D, y.o.Wt, D, &parts, &np) != RG_OK) return -1;
         rg_launch(pdl, rg_rows_res_ln_bf16_kernel, dim3(B), dim3(256), 0, s, parts, np, (size_t)B * D, (const float*)y.o.b, m->px, 1,
