@@ -93,7 +93,7 @@ rg_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int tiles_n = (e.N + TC_BN - 1) / TC_BN, tiles_m = (e.M + TC_BM - 1) / TC_BM;
     const int ntiles = tiles_n * tiles_m;
     const int kb_begin = blockIdx.z * e.kb_per_split;
-    const int nkb = min(e.kb_per_split, e.K / TC_BK - kb_begin);
+    const int nkb = min(e.kb_per_split, (e.K + TC_BK - 1) / TC_BK - kb_begin);  // a ragged last k-block is zero-filled by TMA
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; s++) {
@@ -342,7 +342,9 @@ static __global__ void tc_splitk_reduce_kernel(const float* __restrict__ ws, int
 static rg_status tc_gemm(rg_ctx* ctx, const void* A16, int M, int K, const void* Wt16, int N, float* C, long long ldc,
                          const float* bias, const float* res, long long ldres, int act, const float** raw_parts, int* raw_nparts) {
     const bool raw = raw_parts != nullptr;
-    if (K % TC_BK != 0 || K < TC_BK || M <= 0 || N <= 0) return RG_ERR_UNSUPPORTED;
+    // rows of both operands must start on 16-byte boundaries (K % 8); a last k-block that reaches past K is filled with
+    // zeros by the tensor maps (out-of-bounds fill), on both operands
+    if (K % 8 != 0 || K < TC_BK || M <= 0 || N <= 0) return RG_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(A16) & 15) || (reinterpret_cast<uintptr_t>(Wt16) & 15)) return RG_ERR_UNSUPPORTED;
     if (!g_encode) {
         void* fn = nullptr;
@@ -367,7 +369,7 @@ static rg_status tc_gemm(rg_ctx* ctx, const void* A16, int M, int K, const void*
     CUtensorMap tmA, tmB;
     RG_TRY(tc_make_map(&tmA, A16, M, K));
     RG_TRY(tc_make_map(&tmB, Wt16, N, K));
-    const int nkb = K / TC_BK, ntiles = rg_cdiv(N, TC_BN) * rg_cdiv(M, TC_BM);
+    const int nkb = rg_cdiv(K, TC_BK), ntiles = rg_cdiv(N, TC_BN) * rg_cdiv(M, TC_BM);
     int splits = 1;
     if (M <= TC_BM && ntiles < ctx->sm_count / 2) splits = std::max(1, std::min(nkb / 3, ctx->sm_count / ntiles));  // at least 3 k-blocks per CTA (A/B: 2 and 4 are slower)
     const int kb_per = rg_cdiv(nkb, splits);

@@ -131,6 +131,89 @@ static __global__ void __launch_bounds__(256) rg_tp_allreduce_kernel(rg_tp_ar_ar
 }
 static __global__ void rg_bump_kernel(unsigned* p) { *p += 1u; }
 
+// Row-split projection of the batched token step, tensor parallel: "sum the k-split partial tiles -> all-reduce over the
+// ranks -> + bias + residual -> LayerNorm -> bf16 rows" in ONE kernel (one CTA per row, 256 threads, 8 values per thread
+// at most).  The all-reduce is the one-shot exchange of rg_tp_allreduce_kernel done by the thread that owns the
+// element: its local sum goes, tagged, into slot [parity][rank][row * D + k] of every rank's receive buffer, then the
+// tp_size words of that element are collected from the own buffer (all requested together, bounded) and added in rank
+// order.  Same slots, tags and parities as rg_tp_allreduce_kernel, so both forms of the step can alternate.
+static __global__ void __launch_bounds__(256) rg_rows_res_ln_tp_bf16_kernel(rg_tp_ar_args a, const float* __restrict__ bias,
+                                                                            float* __restrict__ x, const float* __restrict__ gamma,
+                                                                            const float* __restrict__ beta,
+                                                                            __nv_bfloat16* __restrict__ out16, int D) {
+    rg_pdl_sync();
+    __shared__ float sm8[8];
+    const size_t row = blockIdx.x;
+    const unsigned seq = *a.epoch * (unsigned)a.nsites + (unsigned)a.site;
+    const unsigned tag = seq + 1u;
+    const size_t par = seq & 1u;
+    constexpr int PT = RG_ROWS_MAX_D / 256;
+    float v[PT];
+    // local sums out first, for every element of the thread, so that the peers' words travel while the rest is prepared
+#pragma unroll
+    for (int i = 0; i < PT; i++) {
+        const int k = threadIdx.x + i * 256;
+        v[i] = 0.f;
+        if (k < D) {
+            const size_t e = row * D + k;
+            const float part = rg_sum_parts(a.parts + e, a.nparts, a.cnt);
+            const unsigned long long word = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(part);
+            const size_t mine = (par * a.T + a.rank) * a.slot + e;
+            for (int r = 0; r < a.T; r++)
+                asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(a.peer[r] + mine), "l"(word) : "memory");
+        }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < PT; i++) {
+        const int k = threadIdx.x + i * 256;
+        if (k < D) {
+            const size_t e = row * D + k;
+            const unsigned long long* own = a.peer[a.rank] + par * a.T * a.slot + e;
+            float vals[RG_TP_MAX];
+            unsigned pending = (1u << a.T) - 1u, spins = 0;
+            while (pending) {
+                unsigned long long w[RG_TP_MAX];
+#pragma unroll
+                for (int r = 0; r < RG_TP_MAX; r++)
+                    if (r < a.T && (pending & (1u << r)))
+                        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w[r]) : "l"(own + (size_t)r * a.slot) : "memory");
+#pragma unroll
+                for (int r = 0; r < RG_TP_MAX; r++)
+                    if (r < a.T && (pending & (1u << r)) && (unsigned)(w[r] >> 32) == tag) {
+                        vals[r] = __uint_as_float((unsigned)w[r]);
+                        pending &= ~(1u << r);
+                    }
+                if (pending && (++spins > a.limit || ((spins & 1023u) == 0 && *(volatile int*)a.err))) {
+                    *a.err = 1;
+                    break;
+                }
+            }
+            float sum = 0.f;
+#pragma unroll
+            for (int r = 0; r < RG_TP_MAX; r++)
+                if (r < a.T) sum += (pending & (1u << r)) ? 0.f : vals[r];
+            const float t = x[e] + (sum + (bias ? bias[k] : 0.f));
+            x[e] = t;
+            v[i] = t;
+            s += t;
+        }
+    }
+    const float mean = rg_block_sum_256(s, sm8) / (float)D;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < PT; i++) {
+        const int k = threadIdx.x + i * 256;
+        if (k < D) q = fmaf(v[i] - mean, v[i] - mean, q);
+    }
+    const float rstd = 1.f / sqrtf(rg_block_sum_256(q, sm8) / (float)D + 1e-5f);
+#pragma unroll
+    for (int i = 0; i < PT; i++) {
+        const int k = threadIdx.x + i * 256;
+        if (k < D) out16[row * D + k] = __float2bfloat16_rn((v[i] - mean) * rstd * gamma[k] + beta[k]);
+    }
+}
+
 // x[m][n] += t[m][n] + bias[n]
 static __global__ void rg_add_bias_res_kernel(float* __restrict__ x, const float* __restrict__ t,
                                               const float* __restrict__ bias, size_t rows, int N) {
@@ -670,6 +753,7 @@ static rg_status ensure_gather(rg_gpt* m, int rows) {
     dfree(m, m->pgather);
     m->pgather = nullptr, m->pgatherCap = 0;
     RG_TRY(dalloc(m, (void**)&m->pgather, per * (m->tp_size + 1) * 4));
+    RG_CUDA(cudaMemset(m->pgather, 0, per * (m->tp_size + 1) * 4));
     m->pgatherCap = per * (m->tp_size + 1);
     if (m->graph) cudaGraphExecDestroy(m->graph), m->graph = nullptr;
     return RG_OK;
@@ -1057,7 +1141,9 @@ static rg_status step_ready(rg_gpt* m, size_t steps) {
 // k-split partial tiles, the attention kernel sums the q/k/v partials itself, and one kernel per projection does
 // "sum partials + bias (+ residual + next LayerNorm | + activation) -> bf16 rows".  9 launches per block instead of 16.
 static bool rows_tc_usable(const rg_gpt* m) {
-    if (!(m->bf16 && m->use_tc && m->tp_size == 1 && m->pa16) || m->D > RG_ROWS_MAX_D || m->D % 64 || m->F % 64) return false;
+    if (!(m->bf16 && m->use_tc && m->pa16) || m->D > RG_ROWS_MAX_D || m->D % 64 || m->Dl % 8 || m->Fl % 8 || m->Dl < 64 || m->Fl < 64)
+        return false;
+    if (m->tp_size > 1 && !(m->tp_fused && m->Bmax * (size_t)m->D >= 1)) return false;  // tensor parallel: the peer-memory exchange only
     for (const rg_layer& y : m->layers)
         if (!y.qkv.Wt || !y.o.Wt || !y.fc1.Wt || !y.fc2.Wt) return false;
     return m->head.Wt != nullptr;
@@ -1065,12 +1151,34 @@ static bool rows_tc_usable(const rg_gpt* m) {
 static int enqueue_step_rows_tc(rg_gpt* m, int B) {
     cudaStream_t s = m->ctx->stream;
     const uint64_t l0 = m->ctx->launches;
-    const int D = m->D, F = m->F, act = m->cfg.activation;
+    const int D = m->D, Dl = m->Dl, F = m->Fl, act = m->cfg.activation;  // Dl, Fl: this rank's shard (= D, F on one GPU)
+    const bool tp = m->tp_size > 1;
     __nv_bfloat16* a16 = (__nv_bfloat16*)m->pa16;
     // every kernel of the step starts with rg_pdl_sync(): launched with programmatic stream serialization, the launch
     // latency of a kernel overlaps the execution of the one before it (RG_B200_PDL=0 turns the attribute off)
     rg_pdl_scope scope(m->ctx);
     const bool pdl = m->ctx->pdl;
+    if (tp) {
+        rg_bump_kernel<<<1, 1, 0, s>>>(m->d_tp_epoch);  // every rank runs the same steps: the tags of the exchanges agree
+        m->ctx->launches += 1;
+    }
+    // a row-split projection (out-projection: site 0, FC2: site 1 of block l) ends with partial sums on every rank:
+    // on one GPU the rows kernel adds bias + residual and normalises; tensor parallel, it also does the all-reduce
+    auto rows_res_ln = [&](const float* parts_, int np_, const float* bias, const float* gamma, const float* beta, int site) {
+        if (!tp) {
+            rg_launch(pdl, rg_rows_res_ln_bf16_kernel, dim3(B), dim3(256), 0, s, parts_, np_, (size_t)B * D, bias, m->px, 1, gamma, beta,
+                      a16, D);
+        } else {
+            rg_tp_ar_args a;
+            memset(&a, 0, sizeof(a));
+            a.parts = parts_, a.nparts = np_, a.cnt = (size_t)B * D, a.out = nullptr;
+            for (int p = 0; p < m->tp_size; p++) a.peer[p] = m->tp_peer[p];
+            a.T = m->tp_size, a.rank = m->tp_rank, a.slot = (size_t)m->Bmax * m->D;
+            a.epoch = m->d_tp_epoch, a.site = site, a.nsites = 2 * m->L, a.err = m->d_tp_err, a.limit = RG_TP_SPIN_LIMIT;
+            rg_launch(pdl, rg_rows_res_ln_tp_bf16_kernel, dim3(B), dim3(256), 0, s, a, bias, m->px, gamma, beta, a16, D);
+        }
+        RG_LAUNCHED(m->ctx);
+    };
     rg_launch(pdl, rg_embed_step_kernel<__nv_bfloat16>, dim3(B), dim3(128), 0, s, m->tokens, m->C, (const __nv_bfloat16*)m->wte,
               (const __nv_bfloat16*)m->wpe, D, m->ldt, m->px, m->d_pos_next, m->d_pos);
     rg_launch(pdl, rg_rows_res_ln_bf16_kernel, dim3(B), dim3(256), 0, s, nullptr, 0, (size_t)0, nullptr, m->px, 0, m->layers[0].ln1g,
@@ -1082,7 +1190,7 @@ static int enqueue_step_rows_tc(rg_gpt* m, int B) {
     int np = 0;
     for (int l = 0; l < m->L; l++) {
         rg_layer& y = m->layers[l];
-        if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, D, y.qkv.Wt, 3 * D, &parts, &np) != RG_OK) return -1;
+        if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, D, y.qkv.Wt, 3 * Dl, &parts, &np) != RG_OK) return -1;
         {
             rg_attn_step_args a;
             a.qkv_parts = parts, a.nparts = np, a.qkv_bias = y.qkv.b;
@@ -1097,26 +1205,34 @@ static int enqueue_step_rows_tc(rg_gpt* m, int B) {
             else rg_launch(pdl, rg_attn_step_kernel<__nv_bfloat16, 128>, grid, dim3(128), 0, s, a);
             m->ctx->launches += 1;
             if (NS > 1) {
-                rg_launch(pdl, rg_attn_merge_kernel, dim3(rg_cdiv(B * D, 256)), dim3(256), 0, s, (const float*)m->ap, (float*)nullptr, B,
+                rg_launch(pdl, rg_attn_merge_kernel, dim3(rg_cdiv(B * Dl, 256)), dim3(256), 0, s, (const float*)m->ap, (float*)nullptr, B,
                           m->Hl, m->hd, NS, a16);
                 m->ctx->launches += 1;
             }
         }
-        if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, D, y.o.Wt, D, &parts, &np) != RG_OK) return -1;
-        rg_launch(pdl, rg_rows_res_ln_bf16_kernel, dim3(B), dim3(256), 0, s, parts, np, (size_t)B * D, (const float*)y.o.b, m->px, 1,
-                  (const float*)y.ln2g, (const float*)y.ln2b, a16, D);
-        RG_LAUNCHED(m->ctx);
+        if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, Dl, y.o.Wt, D, &parts, &np) != RG_OK) return -1;
+        rows_res_ln(parts, np, y.o.b, y.ln2g, y.ln2b, 2 * l);
         if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, D, y.fc1.Wt, F, &parts, &np) != RG_OK) return -1;
         rg_launch(pdl, rg_rows_act_bf16_kernel, dim3(rg_cdiv((long long)B * F, 256)), dim3(256), 0, s, parts, np, (size_t)B * F,
                   (const float*)y.fc1.b, F, (size_t)B * F, act, a16);
         RG_LAUNCHED(m->ctx);
         if (rg_gemm_bf16_tc_parts(m->ctx, a16, B, F, y.fc2.Wt, D, &parts, &np) != RG_OK) return -1;
         const bool last = l + 1 == m->L;
-        rg_launch(pdl, rg_rows_res_ln_bf16_kernel, dim3(B), dim3(256), 0, s, parts, np, (size_t)B * D, (const float*)y.fc2.b, m->px, 1,
-                  (const float*)(last ? m->lnfg : m->layers[l + 1].ln1g), (const float*)(last ? m->lnfb : m->layers[l + 1].ln1b), a16, D);
+        rows_res_ln(parts, np, y.fc2.b, last ? m->lnfg : m->layers[l + 1].ln1g, last ? m->lnfb : m->layers[l + 1].ln1b, 2 * l + 1);
+    }
+    if (!tp) {
+        if (rg_gemm_bf16_tc(m->ctx, a16, B, D, m->head.Wt, m->V, m->logits, m->V, m->head.b, nullptr, 0, -1) != RG_OK) return -1;
+    } else {
+        // this rank's vocabulary slice -> all-gather of the padded slices -> [B][V] (the gather buffer exists: run_steps
+        // made room for it before the capture)
+        const size_t per = (size_t)B * m->Vpad;
+        float* local = m->pgather + per * m->tp_size;
+        // (the padding columns of `local` are zero since ensure_gather and are never written)
+        if (rg_gemm_bf16_tc(m->ctx, a16, B, D, m->head.Wt, m->Vl, local, m->Vpad, m->head.b, nullptr, 0, -1) != RG_OK) return -1;
+        if (tp_allgather(m, local, m->pgather, per) != RG_OK) return -1;
+        rg_ungather_logits_kernel<<<rg_cdiv((long long)B * m->V, 256), 256, 0, s>>>(m->pgather, m->logits, (size_t)B, m->V, m->Vpad);
         RG_LAUNCHED(m->ctx);
     }
-    if (rg_gemm_bf16_tc(m->ctx, a16, B, D, m->head.Wt, m->V, m->logits, m->V, m->head.b, nullptr, 0, -1) != RG_OK) return -1;
     rg_pick_args pa;
     pa.parts = m->logits, pa.nparts = 1, pa.bias = nullptr, pa.logits = m->logits;
     pa.tokens = m->tokens, pa.picks = m->picks, pa.pos = m->d_pos, pa.pos_next = m->d_pos_next;
