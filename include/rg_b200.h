@@ -211,7 +211,10 @@ RG_API rg_status rg_gpt_trace_read(rg_gpt* m, uint64_t* out, size_t cap_rows, si
  * kernel's waits (0: built-in).  what = 6 (m): CTA 0 of the persistent kernel withholds its q|k|v outputs of block
  * `value` (-1: off).  what = 7 (ctx): runs the tensor-parallel all-reduce kernel as rank 0 of 2 on this GPU with a
  * limit of `value` polls while nothing plays rank 1, and reports the RG_ERR_TIMEOUT that a missing peer produces.
- * The unused handle may be NULL. */
+ * what = 8 (ctx): self-check of the tensor-core projection kernel on a 40 x 200 product with K = `value` (a multiple of
+ * 8 in 64..8192; a K that is not a multiple of the kernel's 64-wide k-blocks exercises the zero-filled last block),
+ * both with its own epilogue and as raw k-split partial tiles, against a float64 dot product; RG_ERR_BACKEND with the
+ * worst difference in rg_last_error() when it is off.  The unused handle may be NULL. */
 RG_API rg_status rg_debug_hook(rg_ctx* ctx, rg_gpt* m, int what, long long value);
 
 /* ---- allocation-free projection ------------------------------------------- */

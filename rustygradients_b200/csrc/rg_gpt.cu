@@ -1649,6 +1649,52 @@ extern "C" rg_status rg_debug_hook(rg_ctx* ctx, rg_gpt* m, int what, long long v
             if (err) return rg_fail(RG_ERR_TIMEOUT, "tensor-parallel all-reduce: a peer's contribution did not arrive in time");
             return RG_OK;
         }
+        case 8: {  // the tensor-core GEMM against a plain dot product: 40 rows, 200 columns, K = value (any multiple of 8 >= 64)
+            if (!ctx || value < 64 || value > 8192 || value % 8) return rg_fail(RG_ERR_INVALID_INPUT, "K must be a multiple of 8 in 64..8192");
+            rg_ctx_guard g(ctx);
+            const int M = 40, N = 200, K = (int)value;
+            std::vector<__nv_bfloat16> ha((size_t)M * K), hw((size_t)N * K);
+            std::vector<float> fa(ha.size()), fw(hw.size());
+            uint32_t st = 12345u;
+            auto next = [&]() { st = st * 1664525u + 1013904223u; return ((float)(st >> 8) * (1.f / 16777216.f) - 0.5f); };
+            for (size_t i = 0; i < ha.size(); i++) ha[i] = __float2bfloat16_rn(next()), fa[i] = __bfloat162float(ha[i]);
+            for (size_t i = 0; i < hw.size(); i++) hw[i] = __float2bfloat16_rn(next()), fw[i] = __bfloat162float(hw[i]);
+            void *da = nullptr, *dw = nullptr;
+            float* dc = nullptr;
+            RG_CUDA(cudaMalloc(&da, std::max<size_t>(ha.size(), (size_t)128 * K) * 2));
+            RG_CUDA(cudaMalloc(&dw, hw.size() * 2));
+            RG_CUDA(cudaMalloc(&dc, (size_t)M * N * 4));
+            RG_CUDA(cudaMemcpy(da, ha.data(), ha.size() * 2, cudaMemcpyHostToDevice));
+            RG_CUDA(cudaMemcpy(dw, hw.data(), hw.size() * 2, cudaMemcpyHostToDevice));
+            std::vector<float> got((size_t)M * N), parts_sum((size_t)M * N, 0.f);
+            rg_status rs = rg_gemm_bf16_tc(ctx, da, M, K, dw, N, dc, N, nullptr, nullptr, 0, -1);
+            if (rs == RG_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rs = RG_ERR_BACKEND;
+            if (rs == RG_OK) cudaMemcpy(got.data(), dc, got.size() * 4, cudaMemcpyDeviceToHost);
+            const float* parts = nullptr;
+            int np = 0;
+            if (rs == RG_OK) rs = rg_gemm_bf16_tc_parts(ctx, da, M, K, dw, N, &parts, &np);
+            if (rs == RG_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rs = RG_ERR_BACKEND;
+            if (rs == RG_OK) {
+                std::vector<float> one((size_t)M * N);
+                for (int z = 0; z < np; z++) {
+                    cudaMemcpy(one.data(), parts + (size_t)z * M * N, one.size() * 4, cudaMemcpyDeviceToHost);
+                    for (size_t i = 0; i < one.size(); i++) parts_sum[i] += one[i];
+                }
+            }
+            cudaFree(da), cudaFree(dw), cudaFree(dc);
+            if (rs != RG_OK) return rg_fail(rs, "tensor-core GEMM self-check: the kernel refused K = %d", K);
+            double worst = 0.0;
+            for (int mi = 0; mi < M; mi++)
+                for (int n = 0; n < N; n++) {
+                    double ref = 0.0;
+                    for (int k = 0; k < K; k++) ref += (double)fa[(size_t)mi * K + k] * (double)fw[(size_t)n * K + k];
+                    worst = std::max(worst, fabs(ref - (double)got[(size_t)mi * N + n]));
+                    worst = std::max(worst, fabs(ref - (double)parts_sum[(size_t)mi * N + n]));
+                }
+            if (!(worst <= 1e-3 * sqrt((double)K)))
+                return rg_fail(RG_ERR_BACKEND, "tensor-core GEMM self-check: K = %d, worst |diff| = %g (%d partial tiles)", K, worst, np);
+            return RG_OK;
+        }
         default:
             return rg_fail(RG_ERR_INVALID_INPUT, "unknown hook %d", what);
     }

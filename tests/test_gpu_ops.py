@@ -184,3 +184,15 @@ def test_attention_from_ops_matches_oracle(backend):
     a = be.reshape(be.transpose(a, 1, 2), [2, 5, 16])
     got = arr(be, lin(a, P[6], P[7]))
     assert np.abs(got - want).max() < 1e-6
+
+
+def test_tensor_core_projection_with_a_ragged_last_k_block(backend):
+    """K need not be a multiple of the kernel's 64-wide k-blocks (a tensor-parallel shard of the hidden layer can be
+    800 wide): the last block is zero-filled by the tensor maps.  The check runs inside the library (rg_debug_hook 8)."""
+    import ctypes as C
+    from rustygradients_b200 import _lib
+    lib = _lib.load()
+    for K in (64, 72, 192, 800, 1600, 3208):
+        _lib.check(lib.rg_debug_hook(backend._ctx, None, 8, K))
+    with pytest.raises(rg.InvalidInput):
+        _lib.check(lib.rg_debug_hook(backend._ctx, None, 8, 100))
