@@ -434,12 +434,75 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 
 # --------------------------------------------------------------------------
 # single small workloads for profiler captures: python bench.py --only decode|prefill|ingest [...]
+# (and, under torchrun, --only tptrace: device trace of the tensor-parallel token loop)
 # (not the benchmark: they print their own JSON line and leave the contract line alone)
 # --------------------------------------------------------------------------
 def _random_params(model, vocab, seed):
     rng = np.random.Generator(np.random.PCG64(seed))
     return [(rng.standard_normal(s, dtype=np.float32) * np.float32(0.02)) if s[0] != 1 or s[1] == vocab
             else np.ones(s, np.float32) for s in model.parameter_shapes()]
+
+
+def run_tp_trace(a) -> None:
+    """Under torchrun: the GPT-2-XL-shape tensor-parallel model of run_tp(), one sequence, and the persistent kernel's
+    own time stamps of the middle block of the last token (rank 0 prints them): per stage, median and latest CTA."""
+    import torch
+    import torch.distributed as dist
+    import rustygradients_b200 as rg
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if world < 2:
+        raise SystemExit("--only tptrace runs under torchrun with 2 or more ranks")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    be = rg.B200Backend(rank)
+    V, D, L, H, P, G = 50257, 1600, 48, 25, 512, 64
+    model = rg.GPTModel(be, rg.GptConfig(1024, V, L, H, D, weight_dtype="bf16", max_batch=4, tp_rank=rank, tp_size=world))
+    prng = np.random.Generator(np.random.PCG64(20245))
+    model.load_parameters([(prng.standard_normal(s, dtype=np.float32) * np.float32(0.02)) if s[0] != 1 or s[1] == V
+                           else np.ones(s, np.float32) for s in model.parameter_shapes()])
+    ident = torch.zeros(128, dtype=torch.uint8, device=dev)
+    if rank == 0:
+        ident = torch.tensor(list(rg.GPTModel.tp_unique_id()), dtype=torch.uint8, device=dev)
+    dist.broadcast(ident, src=0)
+    model.tp_init(bytes(ident.cpu().tolist()))
+    prompt = np.random.Generator(np.random.PCG64(20246)).integers(0, V, size=(1, P), dtype=np.uint32)
+    model.prefill(prompt, want_logits=False)
+    for _ in range(2):
+        model.rewind(P)
+        model.decode_run(G)
+    be.synchronize()
+    dist.barrier()
+    t = time.perf_counter()
+    model.rewind(P)
+    model.decode_run(G)
+    be.synchronize()
+    us = (time.perf_counter() - t) / G * 1e6
+    model.trace(True)
+    model.rewind(P)
+    model.decode_run(G)
+    be.synchronize()
+    tr = model.read_trace(1 << 17).astype(np.int64)
+    if rank == 0:
+        ok = tr[:, 4] > 0
+        blk = L // 2
+        t0 = tr[ok & (tr[:, 3] == blk)][:, 4].min()
+        stages = {}
+        for st, name in enumerate(("qkv", "attention", "out_projection", "fc1", "fc2")):
+            sel = tr[ok & (tr[:, 3] == blk) & (tr[:, 2] == st)]
+            if len(sel):
+                r = (sel[:, 4:8] - t0) / 1e3
+                stages[name] = {"ctas": int(len(sel)),
+                                "median_us": [round(float(np.median(r[:, i])), 2) for i in range(4)],
+                                "latest_us": [round(float(r[:, i].max()), 2) for i in range(4)]}
+        first = tr[ok & (tr[:, 2] == 0)]
+        starts = [np.median(first[first[:, 3] == l][:, 4]) for l in range(L)]
+        print(json.dumps({"only": "tptrace", "tp_size": world, "us_per_token": us, "block": blk,
+                          "columns": ["start", "input ready", "dot products done", "outputs stored"], "stages": stages,
+                          "block_period_us": round(float(np.median(np.diff(starts))) / 1e3, 2)}))
+    dist.barrier()
+    model.close()
+    dist.destroy_process_group()
 
 
 def run_only(a) -> None:
@@ -539,7 +602,7 @@ def main() -> None:
     ap.add_argument("--no-extra", action="store_true", help="skip the batched and tensor-parallel records")
     ap.add_argument("--tokens-per-step", type=int, default=0,
                     help="shorten the decode run (profiling only; the default is the workload's 256)")
-    ap.add_argument("--only", choices=["decode", "prefill", "ingest"],
+    ap.add_argument("--only", choices=["decode", "prefill", "ingest", "tptrace"],
                     help="run one small workload for a profiler capture instead of the benchmark")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=256)
@@ -551,6 +614,9 @@ def main() -> None:
     ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--names", default="hf_gpt2", choices=["hf_gpt2", "rusty"])
     args = ap.parse_args()
+    if args.only == "tptrace":
+        run_tp_trace(args)
+        return
     if args.only:
         run_only(args)
         return
