@@ -38,6 +38,7 @@ if ROOT not in sys.path:
 
 WORKLOAD = "gpt2-small-shape vocab1024 f32 batch1 prompt128 decode256"
 CFG_INDEX = 1
+EXTRAS_BUDGET_S = 360          # time the extra records may take before the headline is printed without them
 NOMINAL_HBM_GBS = 8000.0     # the figure the metric's roofline is defined on
 FALLBACK_HBM_GBS = 6650.0
 NCU_TRAFFIC_RATIO = 1.0036   # measured DRAM bytes (read + write) / algorithmic bytes, profiles/token_loop_kernel_*
@@ -365,20 +366,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     assert int(first_pick[0, 0]) == int(ids_e2e[0, 0])
     all_ids = gather_ids(ids_e2e, world * B, rank, world, dev)   # once, after the loop: the only exchange
     model.close()
-    extra = {}
-    if not args.no_extra:
-        # the headline above is complete at this point: a failure in an extra record is reported inside that record
-        # instead of taking the whole line down (a failure that hits every rank alike, e.g. a wait that ran out)
-        try:
-            extra["batched"] = run_batched(torch, rg, O, be, dev, stream, barrier, rank, world)
-        except rg.RustyGradientsError as e:
-            extra["batched"] = {"error": f"{type(e).__name__}: {e}"}
-        if world > 1:
-            try:
-                extra["tp"] = run_tp(torch, rg, be, dev, stream, barrier, rank, world)
-            except rg.RustyGradientsError as e:
-                extra["tp"] = {"error": f"{type(e).__name__}: {e}"}
-
+    line = None
     if rank == 0:
         tokens = world * B * G * args.steps
         value = tokens / (ms * 1e-3)
@@ -418,14 +406,46 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             "gpu_launches": int(launches), "clocks": clocks,
             "ids_checksum": int(np.asarray(all_ids, dtype=np.uint64).sum()),
         }
-        line.update(extra)
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline:     # host cores only: timed before the extra records use the GPU again
             v, dt = cpu_reference_tokens_per_s(24, params)
             line["cpu_baseline"] = {
                 "value": v, "unit": "tokens/s", "cores": cpu_threads(), "kind": "port", "causal": False,
                 "activation": "relu", "kv_cache": False,
                 "sample": f"24 loop iterations at context lengths spread over 128..383 ({dt:.1f} s): the reference's loop "
                           "(full re-forward per id, no KV cache, unmasked attention, ReLU, all logit rows) in numpy f32 + OpenBLAS"}
+    # ---- extra records (batched, tensor parallel).  The headline above is complete; whatever happens below, it is
+    # printed: a failure that every rank sees is reported inside the record, and if the extras do not finish within
+    # their time budget (a rank stuck in a collective, say) every rank's watchdog ends its process after rank 0 has
+    # printed the line with what was finished until then.
+    extra = {}
+    extras_done = threading.Event()
+
+    def _watchdog():
+        if extras_done.wait(EXTRAS_BUDGET_S):
+            return
+        if rank == 0:
+            out = dict(line)
+            out.update(extra)
+            for key in (("batched", "tp") if world > 1 else ("batched",)):
+                out.setdefault(key, {"error": f"did not finish within {EXTRAS_BUDGET_S} s; the process was ended"})
+            print(json.dumps(out), flush=True)
+        os._exit(0)
+
+    if not args.no_extra:
+        threading.Thread(target=_watchdog, daemon=True).start()
+        try:
+            extra["batched"] = run_batched(torch, rg, O, be, dev, stream, barrier, rank, world)
+        except rg.RustyGradientsError as e:
+            extra["batched"] = {"error": f"{type(e).__name__}: {e}"}
+        if world > 1:
+            try:
+                extra["tp"] = run_tp(torch, rg, be, dev, stream, barrier, rank, world)
+            except rg.RustyGradientsError as e:
+                extra["tp"] = {"error": f"{type(e).__name__}: {e}"}
+        extras_done.set()
+
+    if rank == 0:
+        line.update(extra)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

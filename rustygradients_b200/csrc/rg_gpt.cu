@@ -680,7 +680,7 @@ static rg_status gemm(rg_gpt* m, const float* A, int M, const rg_linear& lin, fl
     p.C = Cout, p.ldc = ldc < 0 ? lin.N : ldc;
     p.M = M, p.N = lin.N, p.K = lin.K;
     p.bias = with_bias ? lin.b : nullptr, p.res = res, p.ldres = lin.N, p.act = act;
-    if (m->bf16 && m->use_tc && lin.Wt && m->pa16 && M >= 8) {
+    if (m->bf16 && m->use_tc && lin.Wt && m->pa16 && M >= 8 && lin.K % 64 == 0) {
         // dense contraction on the tensor cores: bf16 operands (activations rounded on the way in), fp32 accumulate
         const size_t cnt = (size_t)M * lin.K;
         rg_to_bf16_kernel<<<rg_cdiv((long long)cnt, 1024), 256, 0, m->ctx->stream>>>(A, (__nv_bfloat16*)m->pa16, cnt);
@@ -689,7 +689,7 @@ static rg_status gemm(rg_gpt* m, const float* A, int M, const rg_linear& lin, fl
         if (st == RG_OK) return RG_OK;
         if (st != RG_ERR_UNSUPPORTED) return st;
     }
-    if (!m->bf16 && m->use_tc && lin.Wt && m->pa16 && M >= 32) {
+    if (!m->bf16 && m->use_tc && lin.Wt && m->pa16 && M >= 32 && (3 * lin.K) % 64 == 0) {
         // f32 mode with enough rows for a tensor tile: split both operands into bf16 pieces (see lin.Wt) and run the
         // same tcgen05 GEMM over the concatenated K range
         const size_t cnt = (size_t)M * lin.K;
@@ -1141,8 +1141,10 @@ static rg_status step_ready(rg_gpt* m, size_t steps) {
 // k-split partial tiles, the attention kernel sums the q/k/v partials itself, and one kernel per projection does
 // "sum partials + bias (+ residual + next LayerNorm | + activation) -> bf16 rows".  9 launches per block instead of 16.
 static bool rows_tc_usable(const rg_gpt* m) {
-    if (!(m->bf16 && m->use_tc && m->pa16) || m->D > RG_ROWS_MAX_D || m->D % 64 || m->Dl % 8 || m->Fl % 8 || m->Dl < 64 || m->Fl < 64)
-        return false;
+    // Shards whose width is not a multiple of the GEMM's 64-wide k-blocks (hidden shard of 800 columns: GPT-2-XL shape on
+    // 8 GPUs) keep the plain form: the kernel handles such a K (self-check: rg_debug_hook 8), but that configuration has not
+    // been validated end to end on 8 GPUs.
+    if (!(m->bf16 && m->use_tc && m->pa16) || m->D > RG_ROWS_MAX_D || m->D % 64 || m->Dl % 64 || m->Fl % 64) return false;
     if (m->tp_size > 1 && !(m->tp_fused && m->Bmax * (size_t)m->D >= 1)) return false;  // tensor parallel: the peer-memory exchange only
     for (const rg_layer& y : m->layers)
         if (!y.qkv.Wt || !y.o.Wt || !y.fc1.Wt || !y.fc2.Wt) return false;
