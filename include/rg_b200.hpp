@@ -207,6 +207,50 @@ class GPTModel {
     std::shared_ptr<rg_gpt> m_;
 };
 
+// DType and TensorV2 (src/tensor_v2.rs:16-23, 64-83, 85-305): a tensor that knows its device, dtype and whether it
+// requires a gradient.  Like the reference's, every operation forwards to the Backend method of the same name and the
+// result requires a gradient when an operand does; this library computes the forward path only, so no gradient is kept.
+// The data lives on the backend's GPU (the reference's non-CPU arms are `unimplemented!`; here they are the only ones).
+enum class DType { F32, F16, BF16, I32, U32 };
+
+class TensorV2 {
+  public:
+    TensorV2(const B200Backend& be, Storage data, bool requires_grad) : be_(be), data_(std::move(data)), requires_grad_(requires_grad) {}
+    // TensorV2::from_slice / zeros / ones
+    static TensorV2 from_slice(const B200Backend& be, const std::vector<float>& data, const std::vector<size_t>& shape, bool requires_grad) {
+        return TensorV2(be, be.from_slice(data, shape), requires_grad);
+    }
+    static TensorV2 zeros(const B200Backend& be, const std::vector<size_t>& shape, bool requires_grad) { return TensorV2(be, be.zeros(shape), requires_grad); }
+    static TensorV2 ones(const B200Backend& be, const std::vector<size_t>& shape, bool requires_grad) { return TensorV2(be, be.ones(shape), requires_grad); }
+
+    std::vector<size_t> shape() const { return data_.shape(); }
+    DType dtype() const { return DType::F32; }
+    bool requires_grad() const { return requires_grad_; }
+    int device_index() const { return be_.device_index(); }
+    std::vector<float> to_cpu_data() const { return be_.to_vec(data_); }
+    const Storage& storage() const { return data_; }
+
+    TensorV2 add(const TensorV2& o) const { return TensorV2(be_, be_.add(data_, o.data_), requires_grad_ || o.requires_grad_); }
+    TensorV2 sub(const TensorV2& o) const { return TensorV2(be_, be_.sub(data_, o.data_), requires_grad_ || o.requires_grad_); }
+    TensorV2 mul(const TensorV2& o) const { return TensorV2(be_, be_.mul(data_, o.data_), requires_grad_ || o.requires_grad_); }
+    TensorV2 matmul(const TensorV2& o) const { return TensorV2(be_, be_.matmul(data_, o.data_), requires_grad_ || o.requires_grad_); }
+    TensorV2 relu() const { return TensorV2(be_, be_.relu(data_), requires_grad_); }
+    TensorV2 softmax() const { return TensorV2(be_, be_.softmax(data_), requires_grad_); }
+    TensorV2 reshape(const std::vector<size_t>& s) const { return TensorV2(be_, be_.reshape(data_, s), requires_grad_); }
+    TensorV2 transpose(size_t a, size_t b) const { return TensorV2(be_, be_.transpose(data_, a, b), requires_grad_); }
+
+  private:
+    B200Backend be_;
+    Storage data_;
+    bool requires_grad_;
+};
+
+// ops_v2 (src/ops_v2/basic.rs:15, 56, 94; src/ops_v2/matmul.rs:15)
+inline TensorV2 add_op(const TensorV2& a, const TensorV2& b) { return a.add(b); }
+inline TensorV2 mul_op(const TensorV2& a, const TensorV2& b) { return a.mul(b); }
+inline TensorV2 sub_op(const TensorV2& a, const TensorV2& b) { return a.sub(b); }
+inline TensorV2 matmul_op(const TensorV2& a, const TensorV2& b) { return a.matmul(b); }
+
 // trait Tokenizer (src/tokenization/mod.rs): encode / decode / vocab_size
 class Tokenizer {
   public:

@@ -99,6 +99,20 @@ int main() {
         threw = true;
     }
     EXPECT(threw);
+    // TensorV2 / ops_v2: the reference's own unit cases (src/tensor_v2.rs tests, src/ops_v2/basic.rs and matmul.rs tests)
+    {
+        auto a = rg::TensorV2::ones(be, {2, 2}, false), b = rg::TensorV2::ones(be, {2, 2}, true);
+        auto sum = rg::add_op(a, b);
+        EXPECT(sum.shape() == (std::vector<size_t>{2, 2}) && sum.requires_grad() && sum.dtype() == rg::DType::F32);
+        auto sv = sum.to_cpu_data();
+        EXPECT(sv.size() == 4 && sv[0] == 2 && sv[3] == 2);
+        auto prod = rg::mul_op(rg::TensorV2::from_slice(be, {2, 3}, {2}, false), rg::TensorV2::from_slice(be, {4, 5}, {2}, false));
+        auto pv = prod.to_cpu_data();
+        EXPECT(prod.shape() == (std::vector<size_t>{2}) && pv[0] == 8 && pv[1] == 15 && !prod.requires_grad());
+        auto mm = rg::matmul_op(rg::TensorV2::zeros(be, {2, 3, 4}, false), rg::TensorV2::zeros(be, {2, 4, 5}, false));
+        EXPECT(mm.shape() == (std::vector<size_t>{2, 3, 5}));
+        EXPECT(rg::sub_op(sum, a).relu().transpose(0, 1).reshape({4}).shape() == (std::vector<size_t>{4}));
+    }
     std::printf("OK\n");
     return 0;
 }
