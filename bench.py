@@ -244,6 +244,23 @@ def run_batched(torch, rg, O, be, dev, stream, barrier, rank, world):
     return rec
 
 
+def _pooled_params(shapes, vocab, seed):
+    """Synthetic weights for a large model without drawing 1.5 G normals per rank: one pool of N(0, 0.02) values, every
+    tensor a window of it at its own offset (zero-copy views; vectors of shape [1, n] are ones, the LM-head bias excepted,
+    as in the draw this replaces).  Every rank builds the same list from the same seed and keeps its shard of it."""
+    sizes = [int(s[0]) * int(s[1]) for s in shapes]
+    pool_n = max(sizes) + (1 << 22)
+    pool = np.random.Generator(np.random.PCG64(seed)).standard_normal(pool_n, dtype=np.float32) * np.float32(0.02)
+    out, off = [], 0
+    for i, (s, n) in enumerate(zip(shapes, sizes)):
+        if s[0] != 1 or s[1] == vocab:
+            off = (off + 1000003 * (i + 1)) % (pool_n - n + 1)
+            out.append(pool[off:off + n].reshape(s))
+        else:
+            out.append(np.ones(s, np.float32))
+    return out
+
+
 def run_tp(torch, rg, be, dev, stream, barrier, rank, world):
     """GPT-2-XL shape (vocabulary 50257, d_model 1600, 48 layers, 25 heads), bf16, tensor parallel over all ranks."""
     import torch.distributed as dist
@@ -251,11 +268,7 @@ def run_tp(torch, rg, be, dev, stream, barrier, rank, world):
     V, D, L, H, P, G = 50257, 1600, 48, 25, 512, 256
     peak, _ = measured_hbm_peak()
     model = rg.GPTModel(be, rg.GptConfig(1024, V, L, H, D, weight_dtype="bf16", max_batch=32, tp_rank=rank, tp_size=world))
-    prng = np.random.Generator(np.random.PCG64(20245))
-    params = [(prng.standard_normal(s, dtype=np.float32) * np.float32(0.02)) if s[0] != 1 or s[1] == V
-              else np.ones(s, np.float32) for s in model.parameter_shapes()]
-    model.load_parameters(params)                      # every rank keeps its shard of the same full list
-    del params
+    model.load_parameters(_pooled_params(model.parameter_shapes(), V, 20245))   # every rank keeps its shard of the same list
     ident = torch.zeros(128, dtype=torch.uint8, device=dev)
     if rank == 0:
         ident = torch.tensor(list(rg.GPTModel.tp_unique_id()), dtype=torch.uint8, device=dev)
@@ -478,9 +491,7 @@ def run_tp_trace(a) -> None:
     be = rg.B200Backend(rank)
     V, D, L, H, P, G = 50257, 1600, 48, 25, 512, 64
     model = rg.GPTModel(be, rg.GptConfig(1024, V, L, H, D, weight_dtype="bf16", max_batch=4, tp_rank=rank, tp_size=world))
-    prng = np.random.Generator(np.random.PCG64(20245))
-    model.load_parameters([(prng.standard_normal(s, dtype=np.float32) * np.float32(0.02)) if s[0] != 1 or s[1] == V
-                           else np.ones(s, np.float32) for s in model.parameter_shapes()])
+    model.load_parameters(_pooled_params(model.parameter_shapes(), V, 20245))
     ident = torch.zeros(128, dtype=torch.uint8, device=dev)
     if rank == 0:
         ident = torch.tensor(list(rg.GPTModel.tp_unique_id()), dtype=torch.uint8, device=dev)
