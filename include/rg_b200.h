@@ -217,6 +217,18 @@ RG_API rg_status rg_gpt_trace_read(rg_gpt* m, uint64_t* out, size_t cap_rows, si
  * worst difference in rg_last_error() when it is off.  The unused handle may be NULL. */
 RG_API rg_status rg_debug_hook(rg_ctx* ctx, rg_gpt* m, int what, long long value);
 
+/* Diagnostic, no counterpart in the reference, touches no device: builds the op program the persistent token-loop
+ * kernel would run for one tensor-parallel rank (tp_rank of tp_size; 1 for a single GPU) of a model shape
+ * (hidden = 4 * d_model, head size d_model / heads) with `batch` sequences (1, 2 or 4) on a GPU with `sm_count` SMs, and
+ * checks the properties the kernel relies on.  out[8]: context slices per head, most ops of a CTA, ring slots that fit,
+ * shared-memory bytes, CTAs with LM-head work, packed weight bytes, ops in total, number of violations (a projection
+ * column or an attention (sequence, head, slice) covered zero times or twice, a chunk larger than a ring slot, a residual
+ * slice beyond its capacity).  0 ring slots: the program does not fit shared memory and the library would run the step as
+ * separate launches instead.  RG_ERR_INVALID_INPUT / RG_ERR_UNSUPPORTED for shapes outside
+ * the kernel's limits. */
+RG_API rg_status rg_token_loop_plan(int d_model, int heads, int layers, int vocab, int tp_size, int tp_rank, int bf16, int batch,
+                                    int sm_count, long long* out);
+
 /* ---- allocation-free projection ------------------------------------------- */
 /* No counterpart in the reference.  y[N] = x[K] . W[K,N] + bias[N] (bias may be NULL)
  * for a caller that cannot allocate device memory (inside a capture/replay region,

@@ -133,6 +133,7 @@ SIGNATURES = {
     "rg_gpt_trace_enable": (None, [_P, C.c_int]),
     "rg_gpt_trace_read": (None, [_P, C.POINTER(C.c_uint64), _SZ, _SZP]),
     "rg_debug_hook": (None, [_P, _P, C.c_int, C.c_longlong]),
+    "rg_token_loop_plan": (None, [C.c_int] * 9 + [C.POINTER(C.c_longlong)]),
     "rg_linear_row_noalloc": (None, [_P, _P, _P, _P, _SZ, _SZ, _P]),
     "rg_model_metadata_read": (None, [C.c_char_p, C.POINTER(GptConfigC)]),
     "rg_gpt_load_safetensors": (None, [_P, C.c_char_p, C.c_int]),

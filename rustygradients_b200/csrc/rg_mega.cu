@@ -1452,3 +1452,83 @@ rg_status rg_mega_trace(rg_gpt* m, unsigned long long* out, size_t cap_rows, siz
     *n_rows = n;
     return RG_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Host-only check of the token-loop program (no device is touched): builds the per-CTA op lists of one tensor-parallel
+// rank of a model shape exactly as rg_mega_run would and verifies what the kernel relies on.
+// out[0] context slices per head, [1] most ops of a CTA, [2] ring slots that fit, [3] shared memory bytes,
+// [4] CTAs with LM-head work, [5] packed weight bytes, [6] ops in total, [7] number of violations found:
+// a projection column or an attention (sequence, head, slice) that is covered zero times or twice, a chunk larger than a
+// ring slot, a residual slice larger than res_cap.  out[2] = 0 means the program does not fit the SM's shared memory (the
+// library then runs the step as separate launches).
+// ---------------------------------------------------------------------------
+extern "C" rg_status rg_token_loop_plan(int D, int H, int L, int V, int tp_size, int tp_rank, int bf16, int batch, int sm_count,
+                                               long long* out) {
+    if (!out || D <= 0 || H <= 0 || L <= 0 || V <= 0 || tp_size <= 0 || tp_rank < 0 || tp_rank >= tp_size || sm_count <= 0 ||
+        D % H || mg_variant(batch) < 0 || tp_size > H)
+        return rg_fail(RG_ERR_INVALID_INPUT, "rg_token_loop_plan: shape or rank out of range");
+    rg_gpt m;
+    m.D = D, m.H = H, m.hd = D / H, m.L = L, m.V = V, m.F = 4 * D, m.C = 1024, m.Bmax = batch;
+    m.bf16 = bf16 != 0, m.wsize = bf16 ? 2 : 4;
+    m.tp_size = tp_size, m.tp_rank = tp_rank;
+    {   // the shard arithmetic of rg_gpt_create
+        const int T = tp_size, r = tp_rank, F8 = m.F / 8;
+        m.Hl = H / T + (r < H % T ? 1 : 0), m.h0 = r * (H / T) + std::min(r, H % T), m.Dl = m.Hl * m.hd;
+        m.Fl = 8 * (F8 / T + (r < F8 % T ? 1 : 0)), m.f0 = 8 * (r * (F8 / T) + std::min(r, F8 % T));
+        m.Vpad = (rg_cdiv(V, T) + 7) / 8 * 8;
+        m.v0 = std::min(V, r * m.Vpad), m.Vl = std::max(0, std::min(m.Vpad, V - m.v0));
+        if (T == 1) m.Vpad = V;
+    }
+    if (m.Vl <= 0 || m.hd > 128) return rg_fail(RG_ERR_UNSUPPORTED, "rg_token_loop_plan: shape outside the kernel's limits");
+    rg_mega g;
+    g.G = sm_count;
+    mg_build_program(&m, &g, batch);
+    const int B = batch, NQ = mg_nq_for(m.bf16, B);
+    long long bad = 0;
+    int nslot = 0;
+    size_t smem = 0;
+    for (int ns = 6; ns >= 2 && !nslot; ns--) {
+        const size_t need = mg_smem_bytes(&m, B, NQ, ns, g.max_ops, g.max_cd, g.res_cap, tp_size > 1 ? tp_size * g.G : g.n_pick_ctas);
+        if (need <= 227 * 1024) nslot = ns, smem = need;
+    }
+    // coverage: per (type, layer) the column units of all CTAs tile [0, N) exactly once
+    const int Ns[6] = {3 * m.Dl, 0, D, m.Fl, D, m.Vl};
+    for (int l = 0; l <= L; l++) {
+        for (int type : {MG_QKV, MG_OPROJ, MG_FC1, MG_FC2, MG_HEAD}) {
+            if ((type == MG_HEAD) != (l == L)) continue;
+            const int N = Ns[type];
+            std::vector<int> seen((size_t)N, 0);
+            for (const mg_op& op : g.ops) {
+                if (op.type != type || op.layer != l) continue;
+                for (int c = op.q0 * op.uv; c < (op.q0 + op.nq) * op.uv; c++)
+                    if (c < N) seen[(size_t)c]++;
+            }
+            for (int c = 0; c < N; c++)
+                if (seen[(size_t)c] != 1) bad++;
+        }
+        if (l == L) break;
+        std::vector<int> pairs((size_t)B * m.Hl * g.S, 0);
+        for (const mg_op& op : g.ops)
+            if (op.type == MG_ATTN && op.layer == l) {
+                const size_t i = ((size_t)op.nq * m.Hl + op.q0) * g.S + op.aux;
+                if (op.nq >= B || op.q0 >= m.Hl || op.aux >= g.S) bad++;
+                else pairs[i]++;
+            }
+        for (int v : pairs)
+            if (v != 1) bad++;
+    }
+    // every copy of the schedule fits a ring slot
+    for (const mg_cdesc& cd : g.cds)
+        if (cd.kind == 0 && (cd.bytes <= 0 || (size_t)cd.bytes > MG_SLOT_BYTES || (cd.bytes & 15))) bad++;
+    // every CTA's residual slice fits
+    for (int c = 0; c < g.G; c++) {
+        int res = 0;
+        for (int oi = g.cta_off[c]; oi < g.cta_off[c + 1]; oi++)
+            if (g.ops[oi].type == MG_OPROJ && g.ops[oi].layer == 0) res += g.ops[oi].nq * g.ops[oi].uv;
+        if (res > g.res_cap) bad++;
+    }
+    out[0] = g.S, out[1] = g.max_ops, out[2] = nslot, out[3] = (long long)smem, out[4] = g.n_pick_ctas;
+    out[5] = (long long)g.wpack_bytes, out[6] = (long long)g.ops.size(), out[7] = bad;
+    return RG_OK;
+}
+
