@@ -448,12 +448,12 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         threading.Thread(target=_watchdog, daemon=True).start()
         try:
             extra["batched"] = run_batched(torch, rg, O, be, dev, stream, barrier, rank, world)
-        except rg.RustyGradientsError as e:
+        except Exception as e:  # noqa: BLE001  (library errors and torch / NCCL errors alike: the headline is printed either way)
             extra["batched"] = {"error": f"{type(e).__name__}: {e}"}
         if world > 1:
             try:
                 extra["tp"] = run_tp(torch, rg, be, dev, stream, barrier, rank, world)
-            except rg.RustyGradientsError as e:
+            except Exception as e:  # noqa: BLE001  (library errors and torch / NCCL errors alike: the headline is printed either way)
                 extra["tp"] = {"error": f"{type(e).__name__}: {e}"}
         extras_done.set()
 
