@@ -230,3 +230,34 @@ def test_weighted_index_draw_is_the_top_k_0_draw():
     assert np.abs(freq - w / w.sum()).max() < 0.03
     with pytest.raises(ValueError):
         O.weighted_index_sample(np.zeros(4, np.float32), 0.3)
+
+
+def test_folded_layernorm_and_shifted_sums_identities():
+    """The algebra the token-loop kernels rely on, checked in float64 against the oracle's LayerNorm + Linear
+    (src/ops/norm.rs:41-52, src/nn/linear.rs:50-56):
+    LN(x).W + b = rstd * (x.(g*W) - mean * sum_k(g_k W_kn)) + (beta.W + b), and the exact combination of per-warp shifted
+    sums (count, sum(x - c), sum((x - c)^2), shift c) into mean and biased variance."""
+    rng = np.random.default_rng(3)
+    K, N = 768, 40
+    x = rng.standard_normal(K) * 3 + 1.5
+    g, beta = 1 + 0.1 * rng.standard_normal(K), 0.1 * rng.standard_normal(K)
+    W, b = rng.standard_normal((K, N)) * 0.02, rng.standard_normal(N) * 0.02
+    mean, var = x.mean(), x.var()
+    rstd = 1.0 / np.sqrt(var + 1e-5)
+    direct = (((x - mean) * rstd) * g + beta) @ W + b
+    folded = rstd * (x @ (g[:, None] * W) - mean * (g @ W)) + (beta @ W + b)
+    assert np.abs(direct - folded).max() < 1e-12
+    want = O.layernorm_two_pass(x.astype(np.float32)[None, :], g.astype(np.float32), beta.astype(np.float32))[0].astype(np.float64) @ W + b
+    assert np.abs(want - folded).max() < 2e-5
+    # 8 warps, each with its own shift (its first element); combined with the first warp's shift as the common one
+    parts = []
+    for w in range(8):
+        xs = x[w * 32:(w + 1) * 32] if w < 7 else x[7 * 32:]
+        c = xs[0]
+        parts.append((len(xs), (xs - c).sum(), ((xs - c) ** 2).sum(), c))
+    C0 = parts[0][3]
+    S0 = sum(p[0] for p in parts)
+    S1 = sum(p[1] + p[0] * (p[3] - C0) for p in parts)
+    S2 = sum(p[2] + 2 * (p[3] - C0) * p[1] + p[0] * (p[3] - C0) ** 2 for p in parts)
+    m1 = S1 / S0
+    assert abs((C0 + m1) - mean) < 1e-12 and abs((S2 / S0 - m1 * m1) - var) < 1e-10
